@@ -1,0 +1,115 @@
+/*
+ * C ABI of one kernel plugin (libgemm_<config name>.so): Y = X * W^T on one B200.
+ *
+ *   X  row-major M x K      W  row-major N x K      Y  row-major M x N (bf16), fully overwritten
+ *   FP32 accumulation.  All pointers are DEVICE pointers, 16-byte aligned; K and N are
+ *   multiples of 8 elements (16-byte row pitch).  M, N, K need not be multiples of the tile.
+ *
+ * Every plugin exports the same symbols; the configuration (data type, tile, stages, CTA
+ * pairing, split-K, operand swap) is compiled in and encoded in the file name, which is what
+ * the registry parses -- exactly the reference's scheme (src/gemm_config.h:65-120,
+ * CMakeLists.txt:40-60).
+ *
+ * Plain C: no CUDA or C++ types in the signatures, so it binds from dlsym, ctypes, cgo, JNI...
+ */
+#ifndef SM100_GEMM_H
+#define SM100_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t is `struct CUstream_st *`; spelled out so the header needs no CUDA include. */
+typedef struct CUstream_st *gemm_stream_t;
+
+/* Error codes (gemm_run_ex return value, gemm_last_error). */
+enum {
+    GEMM_OK = 0,
+    GEMM_ERR_SHAPE = 1,          /* M/N/K not supported by this configuration              */
+    GEMM_ERR_CUDA = 2,           /* a CUDA runtime call failed (message has the detail)    */
+    GEMM_ERR_DRIVER = 3,         /* tensor-map encoding failed / driver entry point missing */
+    GEMM_ERR_WORKSPACE = 4,      /* split-K workspace missing or too small                 */
+    GEMM_ERR_DEVICE_TIMEOUT = 5, /* a bounded wait inside a kernel gave up                 */
+    GEMM_ERR_ARG = 6             /* null / misaligned pointer, bad struct size, wrong dtype */
+};
+
+/* Data-type families (the `dt` prefix of a configuration name). */
+enum {
+    GEMM_DT_BF16 = 0,  /* X, W bf16                                                        */
+    GEMM_DT_FP8 = 1,   /* X, W e4m3, one FP32 scale per tensor                             */
+    GEMM_DT_MXFP8 = 2, /* X, W e4m3, one ue8m0 scale per 32 K-elements                     */
+    GEMM_DT_W4A16 = 3, /* X bf16; W signed int4 (2 per byte, low nibble = even k), bf16    */
+                       /* scale per `group_size` K-elements                                */
+    GEMM_DT_W4A4 = 4   /* X, W e2m1 (2 per byte), one ue8m0 scale per 32 K-elements        */
+};
+
+/*
+ * Replaces: extern "C" void gemm_run(...) of the reference, src/kernel_entry.cu.in:14-27
+ * (typedef GemmKernelFn, src/gemm_config.h:20-22; found with dlsym "gemm_run",
+ * src/gemm_config.h:93).  Same symbol, same argument list, same meaning: BF16 operands,
+ * stream-ordered and asynchronous, `workspace` used only by split-K configurations
+ * (>= gemm_workspace_bytes(M,N,K) bytes, need not be zeroed; the reference asks for
+ * SPLIT_K*M*N floats, src/bf16_gemm.cuh:601).
+ * Unlike the reference it never calls exit() and never throws: on failure nothing is
+ * launched and the error is kept for gemm_last_error() on the calling thread.
+ * Only plugins whose data type is bf16 accept this call; the others report GEMM_ERR_ARG.
+ */
+void gemm_run(int M, int N, int K, const void *X, const void *W, void *Y, float *workspace, gemm_stream_t stream);
+
+/*
+ * Extended arguments for every data type.  No counterpart in the reference (it is
+ * BF16-only); gemm_run(M,N,K,X,W,Y,ws,stream) == gemm_run_ex with dtype GEMM_DT_BF16.
+ */
+typedef struct GemmArgs {
+    uint32_t struct_size;   /* sizeof(GemmArgs), checked                                   */
+    uint32_t dtype;         /* GEMM_DT_*; must match the plugin                            */
+    int32_t M, N, K;
+    int32_t group_size;     /* W4A16: K-elements per scale (128); others: ignored          */
+    const void *X;          /* activations, layout per dtype                               */
+    const void *W;          /* weights, layout per dtype                                   */
+    void *Y;                /* bf16 M x N                                                  */
+    const void *x_scale;    /* MXFP8 / W4A4: ue8m0 [M][K/32]; else NULL                    */
+    const void *w_scale;    /* MXFP8 / W4A4: ue8m0 [N][K/32]; W4A16: bf16 [N][K/group]     */
+    float x_scale_f;        /* FP8: per-tensor scale of X (1.0 elsewhere)                  */
+    float w_scale_f;        /* FP8: per-tensor scale of W (1.0 elsewhere)                  */
+    void *workspace;        /* split-K partial sums; may be NULL when not needed           */
+    size_t workspace_bytes;
+    int32_t sm_limit;       /* 0 = all SMs; >0 = persistent grid uses at most this many    */
+    int32_t reserved;
+    gemm_stream_t stream;
+} GemmArgs;
+
+/* Returns GEMM_OK or an error code; asynchronous on success. */
+int gemm_run_ex(const GemmArgs *args);
+
+/* The configuration name compiled into this plugin ("bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0"). */
+const char *gemm_config_name(void);
+
+/* Bytes of workspace the configuration needs for this shape (0 when it needs none).
+ * The reference leaves this to the caller, who passes 4*M*N floats (src/bench.cu:377). */
+size_t gemm_workspace_bytes(int M, int N, int K);
+
+/* 1 when the configuration can run the shape (the reference's GemmConfig::is_valid_for,
+ * src/gemm_config.h:34-38, answered by the plugin itself). */
+int gemm_can_run(int M, int N, int K);
+
+/* Dynamic shared memory the kernel asks for (the reference models this in
+ * GemmConfig::smem_bytes, src/gemm_config.h:40-45). */
+size_t gemm_smem_bytes(void);
+
+/* Error of the last gemm_run / gemm_run_ex on this thread, and its text. */
+int gemm_last_error(void);
+const char *gemm_last_error_message(void);
+
+/* Synchronises the current device and reports whether any kernel of this plugin abandoned a
+ * wait (GEMM_ERR_DEVICE_TIMEOUT) since the last check.  The reference's kernels spin without
+ * limit (src/bf16_gemm.cuh:137-148), so it has nothing to report. */
+int gemm_check_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SM100_GEMM_H */

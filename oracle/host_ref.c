@@ -1,0 +1,321 @@
+/*
+ * CPU oracle for Y = X * W^T (X row-major MxK, W row-major NxK, FP32 accumulate).
+ *
+ * THIS IS TEST INFRASTRUCTURE, NOT PRODUCT CODE.  Only the test-suite, the smoke
+ * check and the benchmark's CPU-baseline leg may call it; the GPU library never does.
+ *
+ * Parity status: the reference project ships no golden vectors, known-answer files
+ * or host GEMM.  Its check is a GPU kernel whose loop body is
+ *     acc = 0; for k in 0..K-1: acc += float(X[row*K+k]) * float(W[col*K+k]); Y[row*N+col] = acc
+ * (reference src/bench.cu:68-85, loop at :77-84).  This file restates that loop on
+ * the host.  The strict mode keeps the k-ascending FP32 order exactly; the fast mode
+ * lets the compiler reorder the additions inside one dot product (vector lanes),
+ * which is inside the rounding noise the tolerances allow.  The restatement is
+ * pinned by hand-computable known answers and by fixtures under tests/golden/
+ * that were produced by an independent float64 computation.
+ *
+ * The quantised variants (FP8 e4m3 per-tensor, MXFP8, W4A16, W4A4/MX-FP4) have no
+ * counterpart in the reference at all ("parity unpinned" by the reference); their
+ * oracle is "dequantise on the host, then the same FP32 GEMM", as the task states.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+static inline float bf16_to_f32(uint16_t v)
+{
+    uint32_t u = (uint32_t)v << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* round-to-nearest-even float -> bf16, NaN kept quiet (matches __float2bfloat16_rn) */
+static inline uint16_t f32_to_bf16(float f)
+{
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u)
+        return (uint16_t)((u >> 16) | 0x0040u);
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+int oracle_num_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+void oracle_bf16_to_f32(const uint16_t *src, float *dst, size_t n)
+{
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t i = 0; i < (ptrdiff_t)n; i++)
+        dst[i] = bf16_to_f32(src[i]);
+}
+
+void oracle_f32_to_bf16(const float *src, uint16_t *dst, size_t n)
+{
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t i = 0; i < (ptrdiff_t)n; i++)
+        dst[i] = f32_to_bf16(src[i]);
+}
+
+/* one dot product, strict k-ascending FP32 order: reference src/bench.cu:77-84 */
+static float dot_strict(const float *x, const float *w, int K)
+{
+    volatile float acc = 0.0f; /* volatile: no reassociation, no vectorisation */
+    for (int k = 0; k < K; k++) {
+        float p = x[k] * w[k];
+        acc = acc + p;
+    }
+    return acc;
+}
+
+/*
+ * Y[rows[i], :] for i < n_rows (rows == NULL means rows 0..n_rows-1), FP32 operands.
+ * Fast mode: 4 output columns at a time so each X row segment is reused from
+ * registers/L1; additions inside a dot product are reordered across SIMD lanes only.
+ */
+void oracle_gemm_f32_rows(int N, int K, const float *X, const float *W, float *Y,
+                          const int *rows, int n_rows, int strict)
+{
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int i = 0; i < n_rows; i++) {
+        int r = rows ? rows[i] : i;
+        const float *x = X + (size_t)r * K;
+        float *y = Y + (size_t)i * N;
+        if (strict) {
+            for (int c = 0; c < N; c++)
+                y[c] = dot_strict(x, W + (size_t)c * K, K);
+            continue;
+        }
+        int c = 0;
+        for (; c + 4 <= N; c += 4) {
+            const float *w0 = W + (size_t)c * K, *w1 = w0 + K, *w2 = w1 + K, *w3 = w2 + K;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma omp simd reduction(+ : a0, a1, a2, a3)
+            for (int k = 0; k < K; k++) {
+                float xv = x[k];
+                a0 += xv * w0[k];
+                a1 += xv * w1[k];
+                a2 += xv * w2[k];
+                a3 += xv * w3[k];
+            }
+            y[c] = a0; y[c + 1] = a1; y[c + 2] = a2; y[c + 3] = a3;
+        }
+        for (; c < N; c++) {
+            const float *w0 = W + (size_t)c * K;
+            float a0 = 0.f;
+#pragma omp simd reduction(+ : a0)
+            for (int k = 0; k < K; k++)
+                a0 += x[k] * w0[k];
+            y[c] = a0;
+        }
+    }
+}
+
+/*
+ * bf16 in, FP32 out.  The reference's oracle signature (src/bench.cu:87-95:
+ * naive_gemm_f32(M,N,K,X,W,Y)) with two additions: a row list and the strict flag.
+ * Returns 0, or -1 when scratch memory cannot be had.
+ */
+int oracle_gemm_bf16_rows(int M, int N, int K, const uint16_t *X, const uint16_t *W,
+                          float *Y, const int *rows, int n_rows, int strict)
+{
+    (void)M;
+    float *Wf = (float *)malloc((size_t)N * K * sizeof(float));
+    float *Xf = (float *)malloc((size_t)n_rows * K * sizeof(float));
+    if (!Wf || !Xf) { free(Wf); free(Xf); return -1; }
+    oracle_bf16_to_f32(W, Wf, (size_t)N * K);
+    for (int i = 0; i < n_rows; i++) {
+        int r = rows ? rows[i] : i;
+        for (int k = 0; k < K; k++)
+            Xf[(size_t)i * K + k] = bf16_to_f32(X[(size_t)r * K + k]);
+    }
+    oracle_gemm_f32_rows(N, K, Xf, Wf, Y, NULL, n_rows, strict);
+    free(Wf); free(Xf);
+    return 0;
+}
+
+int oracle_gemm_bf16(int M, int N, int K, const uint16_t *X, const uint16_t *W, float *Y, int strict)
+{
+    return oracle_gemm_bf16_rows(M, N, K, X, W, Y, NULL, M, strict);
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Number formats of the quantised variants (no reference counterpart; OCP MX v1.0 and the
+ * OFP8 e4m3 "fn" format: no infinities, 0x7f/0xff = NaN, max finite 448).
+ * ---------------------------------------------------------------------------------------- */
+
+float oracle_e4m3_to_f32(uint8_t v)
+{
+    int s = v >> 7, e = (v >> 3) & 0xf, m = v & 7;
+    float r;
+    if (e == 0xf && m == 7) return NAN;
+    if (e == 0) r = ldexpf((float)m, -9);           /* subnormal: m/8 * 2^-6 */
+    else r = ldexpf((float)(8 + m), e - 7 - 3);
+    return s ? -r : r;
+}
+
+/* round-to-nearest-even, saturating to +-448 (satfinite), NaN -> 0x7f */
+uint8_t oracle_f32_to_e4m3(float f)
+{
+    if (isnan(f)) return 0x7f;
+    uint8_t s = signbit(f) ? 0x80 : 0;
+    float a = fabsf(f);
+    if (a >= 464.0f) return s | 0x7e;                /* beyond the midpoint above 448: saturate */
+    if (a < ldexpf(1.0f, -10)) return s;             /* below half the smallest subnormal */
+    int e;
+    (void)frexpf(a, &e);                             /* a = f * 2^e, f in [0.5,1) */
+    int E = e - 1;                                   /* a in [2^E, 2^(E+1)) */
+    if (E < -6) E = -6;                              /* subnormal range shares exponent -6 */
+    float q = ldexpf(a, 3 - E);                      /* units of the 3-bit mantissa step */
+    float rq = nearbyintf(q);                        /* RNE in the default rounding mode */
+    int qi = (int)rq;
+    if (qi >= 16) { qi = 8; E += 1; }                /* mantissa overflow */
+    uint8_t bits;
+    if (E == -6 && qi < 8) bits = (uint8_t)qi;       /* subnormal */
+    else bits = (uint8_t)(((E + 7) << 3) | (qi - 8));
+    if (bits > 0x7e) bits = 0x7e;
+    return s | bits;
+}
+
+/* e2m1 (FP4): values +-{0, .5, 1, 1.5, 2, 3, 4, 6} */
+static const float E2M1_LUT[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+
+float oracle_e2m1_to_f32(uint8_t v)
+{
+    float r = E2M1_LUT[v & 7];
+    return (v & 8) ? -r : r;
+}
+
+/* round-to-nearest, ties to the even code, saturating at 6 */
+uint8_t oracle_f32_to_e2m1(float f)
+{
+    uint8_t s = signbit(f) ? 8 : 0;
+    float a = fabsf(f);
+    if (isnan(a)) return s | 7;
+    uint8_t best = 0;
+    float bd = INFINITY;
+    for (uint8_t c = 0; c < 8; c++) {
+        float d = fabsf(a - E2M1_LUT[c]);
+        if (d < bd || (d == bd && (c & 1) == 0)) { bd = d; best = c; }
+    }
+    return s | best;
+}
+
+/* ue8m0: value 2^(v-127); 0xff = NaN */
+float oracle_ue8m0_to_f32(uint8_t v)
+{
+    if (v == 0xff) return NAN;
+    return ldexpf(1.0f, (int)v - 127);
+}
+
+/* smallest power of two >= amax/elem_max (so the scaled block fits), clamped to the format */
+uint8_t oracle_ue8m0_for_block(float amax, float elem_max)
+{
+    if (!(amax > 0.f)) return 127;                   /* all-zero block: scale 1 */
+    float t = amax / elem_max;
+    int e;
+    float m = frexpf(t, &e);                         /* t = m * 2^e, m in [0.5,1) */
+    int p = (m == 0.5f) ? e - 1 : e;                 /* ceil(log2 t) */
+    p += 127;
+    if (p < 0) p = 0;
+    if (p > 254) p = 254;
+    return (uint8_t)p;
+}
+
+/*
+ * MX quantisation of a row-major R x K matrix along K in blocks of 32:
+ *   kind 8: elements e4m3 (1 byte each),   out_elems has R*K bytes
+ *   kind 4: elements e2m1, two per byte (low nibble = even k), out_elems has R*K/2 bytes
+ * scales: R x K/32 ue8m0 bytes, row-major.
+ */
+void oracle_mx_quantise(const float *src, int R, int K, int kind, uint8_t *out_elems, uint8_t *scales)
+{
+    const float emax = (kind == 8) ? 448.0f : 6.0f;
+    int KB = K / 32;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < R; r++) {
+        for (int b = 0; b < KB; b++) {
+            const float *p = src + (size_t)r * K + b * 32;
+            float amax = 0.f;
+            for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(p[i]));
+            uint8_t sc = oracle_ue8m0_for_block(amax, emax);
+            scales[(size_t)r * KB + b] = sc;
+            float inv = ldexpf(1.0f, 127 - (int)sc);
+            if (kind == 8) {
+                for (int i = 0; i < 32; i++)
+                    out_elems[(size_t)r * K + b * 32 + i] = oracle_f32_to_e4m3(p[i] * inv);
+            } else {
+                for (int i = 0; i < 32; i += 2) {
+                    uint8_t lo = oracle_f32_to_e2m1(p[i] * inv);
+                    uint8_t hi = oracle_f32_to_e2m1(p[i + 1] * inv);
+                    out_elems[((size_t)r * K + b * 32 + i) / 2] = (uint8_t)(lo | (hi << 4));
+                }
+            }
+        }
+    }
+}
+
+void oracle_mx_dequantise(const uint8_t *elems, const uint8_t *scales, int R, int K, int kind, float *dst)
+{
+    int KB = K / 32;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < R; r++) {
+        for (int k = 0; k < K; k++) {
+            float s = oracle_ue8m0_to_f32(scales[(size_t)r * KB + k / 32]);
+            float v;
+            if (kind == 8) v = oracle_e4m3_to_f32(elems[(size_t)r * K + k]);
+            else {
+                uint8_t byte = elems[((size_t)r * K + k) / 2];
+                v = oracle_e2m1_to_f32((k & 1) ? (byte >> 4) : (byte & 0xf));
+            }
+            dst[(size_t)r * K + k] = v * s;
+        }
+    }
+}
+
+/* per-tensor e4m3: q = e4m3(src / scale) */
+void oracle_e4m3_quantise(const float *src, size_t n, float scale, uint8_t *dst)
+{
+    float inv = 1.0f / scale;
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t i = 0; i < (ptrdiff_t)n; i++)
+        dst[i] = oracle_f32_to_e4m3(src[i] * inv);
+}
+
+void oracle_e4m3_dequantise(const uint8_t *src, size_t n, float scale, float *dst)
+{
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t i = 0; i < (ptrdiff_t)n; i++)
+        dst[i] = oracle_e4m3_to_f32(src[i]) * scale;
+}
+
+/*
+ * W4A16 weights: signed int4 in [-8,7], two per byte along K (low nibble = even k),
+ * one bf16 scale per `group` K-elements: w[n,k] = q[n,k] * float(scale[n, k/group]).
+ */
+void oracle_int4_dequantise(const uint8_t *packed, const uint16_t *scales, int N, int K, int group, float *dst)
+{
+    int G = K / group;
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; n++) {
+        for (int k = 0; k < K; k++) {
+            uint8_t byte = packed[((size_t)n * K + k) / 2];
+            int q = (k & 1) ? (byte >> 4) : (byte & 0xf);
+            if (q >= 8) q -= 16;
+            dst[(size_t)n * K + k] = (float)q * bf16_to_f32(scales[(size_t)n * G + k / group]);
+        }
+    }
+}

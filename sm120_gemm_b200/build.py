@@ -1,0 +1,90 @@
+"""Builds the kernel plugins (one shared library per configuration) with nvcc for sm_100a.
+
+Same job as the reference's CMake loop (CMakeLists.txt:13-60: run the generator, configure
+kernel_entry.cu.in once per configuration, add_library(SHARED) each), done with direct nvcc
+calls so no CMake is needed: the configuration reaches csrc/kernel_entry.cu as -D macros.
+
+    python -m sm120_gemm_b200.build            # all configurations, in parallel
+    python -m sm120_gemm_b200.build --only bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+from .gen_configs import GemmConfig, generate_configs
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+KERNEL_DIR = os.path.join(HERE, "kernels")
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+              "-Xcompiler", "-fPIC", "-ccbin", "/usr/bin/g++", "-diag-suppress", "177"]
+
+
+def entry_source(cfg: GemmConfig) -> str:
+    return os.path.join(CSRC, "kernel_entry.cu")
+
+
+def plugin_path(cfg: GemmConfig) -> str:
+    return os.path.join(KERNEL_DIR, f"libgemm_{cfg.name()}.so")
+
+
+def _deps_mtime() -> float:
+    newest = 0.0
+    for root in (CSRC, os.path.join(HERE, "..", "include")):
+        for f in os.listdir(root):
+            if f.endswith((".cu", ".cuh", ".h")):
+                newest = max(newest, os.path.getmtime(os.path.join(root, f)))
+    return newest
+
+
+def build_one(cfg: GemmConfig, force: bool = False, verbose: bool = False) -> str:
+    out = plugin_path(cfg)
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= _deps_mtime():
+        return out
+    os.makedirs(KERNEL_DIR, exist_ok=True)
+    cmd = [NVCC, *NVCC_FLAGS, *cfg.defines(), "-o", out, entry_source(cfg)]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {cfg.name()}:\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        sys.stderr.write(r.stderr)
+    return out
+
+
+def build_all(configs=None, force: bool = False, jobs: int | None = None) -> list[str]:
+    configs = list(configs) if configs is not None else generate_configs()
+    jobs = jobs or max(1, (os.cpu_count() or 2))
+    with ThreadPoolExecutor(jobs) as ex:
+        return list(ex.map(lambda c: build_one(c, force), configs))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", action="append", help="configuration name (repeatable)")
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("-v", "--verbose", action="store_true", help="print ptxas register / spill report")
+    args = ap.parse_args()
+    if args.only:
+        cfgs = []
+        for n in args.only:
+            c = GemmConfig.parse(n)
+            if c is None:
+                sys.exit(f"cannot parse configuration name {n!r}")
+            cfgs.append(c)
+        for c in cfgs:
+            print(build_one(c, args.force, args.verbose))
+    else:
+        outs = build_all(force=args.force)
+        print(f"built {len(outs)} plugins in {KERNEL_DIR}")
+
+
+if __name__ == "__main__":
+    main()

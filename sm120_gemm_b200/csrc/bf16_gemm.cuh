@@ -1,0 +1,528 @@
+// Y = X * W^T for sm_100a: TMA -> 128B-swizzled shared-memory ring -> tcgen05.mma with the
+// accumulator in TMEM -> epilogue out of TMEM.  One persistent kernel template serves the
+// direct path, split-K (FP32 partials) and the dense FP8 per-tensor variant (same pipeline,
+// 1-byte elements, kind::f8f6f4).
+//
+// Plays the role of the reference's src/bf16_gemm.cuh (kernels :259-503 and :606-828, host
+// launchers BF16GemmMMA::run :506-542 and BF16GemmMMASplitK::run :849-896), which is a
+// warpgroup mma.sync design for sm_120a.  Nothing of that structure is kept except the
+// class names of the entry points and the persistent static tile loop.
+//
+// Warp roles inside one CTA (256 threads):
+//   warp 0    TMA producer (one lane)          warp 1    tcgen05.mma issuer (one lane)
+//   warp 2    TMEM allocation / release        warp 3    idle
+//   warps 4-7 epilogue: warp w reads TMEM lanes 32*(w-4) .. +31 (one output row per thread)
+//
+// Barriers:  full[s]   TMA bytes landed           -> MMA issuer
+//            empty[s]  tcgen05.commit of stage s  -> producer
+//            tfull[a]  tcgen05.commit of a tile   -> epilogue       (a = accumulator buffer 0/1)
+//            tempty[a] epilogue drained buffer a  -> MMA issuer
+// Two accumulator buffers let the epilogue of tile t overlap the main loop of tile t+1.
+//
+// CTA pairs (CG = 2): two CTAs of a cluster compute one 256 x BN tile.  Each loads its own
+// 128 rows of X and its own BN/2 rows of W (no multicast), the leader CTA issues one
+// cta_group::2 MMA that reads both shared memories, and each CTA ends up with its 128 rows of
+// the accumulator in its own TMEM.  full[] lives in the leader and counts both CTAs' bytes;
+// empty[] / tfull[] arrivals are delivered to both CTAs by the commit.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "gemm_host.h"
+#include "ptx_sm100.cuh"
+#include "umma_desc.h"
+
+using bf16 = __nv_bfloat16;
+
+namespace sm100 {
+
+enum : int { OPK_BF16 = 0, OPK_E4M3 = 1 };      // operand element kind of the dense kernel
+enum : int { EPI_DIRECT = 0, EPI_TMA = 1 };     // epilogue: register->global stores, or smem + TMA store
+
+struct GemmParams {
+    int M, N, K;
+    int num_m_blocks, num_n_blocks;
+    int num_k_blocks;     // per split
+    int group_n;          // width (in N tiles) of a rasterisation band
+    void *Y;              // bf16 output (direct epilogue)
+    float *workspace;     // split-K partial sums [split][M][N]
+    float alpha;          // epilogue scale (FP8 per-tensor: sx*sw)
+    uint32_t *status;
+};
+
+// Tile order: bands of `group_n` tile columns, walked row by row inside a band, so the CTAs
+// running at one time cover a compact block of Y and share X and W tiles through L2.
+// (Same purpose as the reference's rasterize_tile, src/bf16_gemm.cuh:225-237.)
+__host__ __device__ __forceinline__ void tile_to_mn(int tile, int num_m, int num_n, int group_n, int &mb, int &nb)
+{
+    int per_band = group_n * num_m;
+    int band = tile / per_band;
+    int rem = tile - band * per_band;
+    int n_first = band * group_n;
+    int width = num_n - n_first < group_n ? num_n - n_first : group_n;
+    mb = rem / width;
+    nb = n_first + (rem - mb * width);
+}
+
+template <int OPK_, int BN_, int STAGES_, int CG_, int SPLIT_K_, int EPI_>
+struct UmmaGemmTraits {
+    static constexpr int OPK = OPK_;
+    static constexpr int BN = BN_;
+    static constexpr int STAGES = STAGES_;
+    static constexpr int CG = CG_;
+    static constexpr int SPLIT_K = SPLIT_K_;
+    static constexpr int EPI = (SPLIT_K_ > 1) ? EPI_DIRECT : EPI_;
+    static constexpr int ELEM_BYTES = (OPK_ == OPK_BF16) ? 2 : 1;
+    static constexpr int BM_CTA = 128;                     // rows of X (and of the accumulator) per CTA
+    static constexpr int BM = BM_CTA * CG_;                // rows of the tile
+    static constexpr int BK_BYTES = 128;                   // one swizzle span per row
+    static constexpr int BK = BK_BYTES / ELEM_BYTES;       // K elements per stage
+    static constexpr int UMMA_K_STEPS = BK_BYTES / 32;     // 4 MMAs per stage
+    static constexpr int BN_CTA = BN_ / CG_;               // rows of W this CTA loads
+    static constexpr int A_BYTES = BM_CTA * BK_BYTES;
+    static constexpr int B_BYTES = BN_CTA * BK_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int OUT_CHUNK = 64;                   // output columns per TMA store (128 bytes of bf16)
+    static constexpr int STAGING_BYTES = (EPI == EPI_TMA) ? 2 * BM_CTA * OUT_CHUNK * 2 : 0;
+    static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4;
+    static constexpr int SMEM_BYTES = STAGES_ * STAGE_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + 16;
+    static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;   // slack to align the base to 1024 bytes
+    static constexpr int ACC_COLS = 2 * BN_;               // two FP32 accumulator buffers
+    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
+    static constexpr int THREADS = 256;
+    static_assert(BN_ % 64 == 0 && BN_ >= 64 && BN_ <= 256, "BN must be 64, 128, 192 or 256");
+    static_assert(CG_ == 1 || CG_ == 2, "CTA group is 1 or 2");
+    static_assert(STAGES_ >= 2, "at least two ring stages");
+    static_assert(SMEM_ALLOC <= 232448, "exceeds the 227 KB of shared memory one CTA can have");
+};
+
+template <class T>
+__global__ void __launch_bounds__(256, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                 const __grid_constant__ CUtensorMap tmap_y, const GemmParams p)
+{
+    constexpr int CG = T::CG;
+    constexpr int BN = T::BN;
+    constexpr int STAGES = T::STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (smem_base - raw_addr);
+
+    const uint32_t a_base = smem_base;
+    const uint32_t b_base = smem_base + STAGES * T::A_BYTES;
+    const uint32_t stg_base = b_base + STAGES * T::B_BYTES;
+    const uint32_t bar_base = stg_base + T::STAGING_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (bar_base - smem_base) + 8u * T::NUM_BARRIERS);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+    const int cluster_id = blockIdx.x / CG;
+    const int num_clusters = gridDim.x / CG;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), CG * 4);   // one arrival per epilogue warp of every CTA of the group
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tensormap(&tmap_x);
+        prefetch_tensormap(&tmap_w);
+        if (T::EPI == EPI_TMA) prefetch_tensormap(&tmap_y);
+    }
+    if (warp == 2) {
+        tmem_alloc<CG>(smem_u32(tmem_slot), T::TMEM_COLS);
+        tmem_relinquish<CG>();
+    }
+    tc_fence_before_sync();
+    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = p.num_m_blocks * p.num_n_blocks * T::SPLIT_K;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            const uint32_t full_leader = (CG == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
+            bool ok = true;
+            for (int v = cluster_id; v < total_tiles && ok; v += num_clusters) {
+                const int tile = v / T::SPLIT_K, split = v - tile * T::SPLIT_K;
+                int mb, nb;
+                tile_to_mn(tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
+                const int row_x = mb * T::BM + (int)cta_rank * T::BM_CTA;
+                const int row_w = nb * BN + (int)cta_rank * T::BN_CTA;
+                const int kb0 = split * p.num_k_blocks;
+                for (int kb = 0; kb < p.num_k_blocks; kb++) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, stage)) {
+                        ok = false;
+                        break;
+                    }
+                    const int kx = (kb0 + kb) * T::BK;
+                    if constexpr (CG == 1) {
+                        mbar_arrive_expect_tx(full_bar(stage), T::STAGE_BYTES);
+                        tma_load_2d(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x);
+                        tma_load_2d(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w);
+                    } else {
+                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
+                        const uint32_t fb = full_leader + 8u * stage;
+                        tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x);
+                        tma_load_2d_pair(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && cta_rank == 0) {
+            const uint32_t instr = (T::OPK == OPK_BF16) ? make_idesc(UMMA_BF16, UMMA_BF16, T::BM, BN)
+                                                         : make_idesc(UMMA_E4M3, UMMA_E4M3, T::BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int titer = 0;
+            bool ok = true;
+            for (int v = cluster_id; v < total_tiles && ok; v += num_clusters, titer++) {
+                const int acc = titer & 1;
+                const uint32_t acc_phase = (titer >> 1) & 1;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, acc)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < p.num_k_blocks; kb++) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint64_t a_desc = make_smem_desc_k128(a_base + stage * T::A_BYTES);
+                    const uint64_t b_desc = make_smem_desc_k128(b_base + stage * T::B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < T::UMMA_K_STEPS; k++) {
+                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        if constexpr (T::OPK == OPK_BF16)
+                            umma_f16<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, accumulate);
+                        else
+                            umma_f8f6f4<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, accumulate);
+                    }
+                    if constexpr (CG == 1) umma_commit(empty_bar(stage)); else umma_commit_pair(empty_bar(stage), 3);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                if constexpr (CG == 1) umma_commit(tfull_bar(acc)); else umma_commit_pair(tfull_bar(acc), 3);
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ epilogue
+        const int q = warp - 4;                    // TMEM lane quarter this warp may read
+        const int row_in_tile = q * 32 + lane;     // accumulator row = TMEM lane
+        const int epi_tid = threadIdx.x - 128;
+        const uint32_t tempty_leader = (CG == 2) ? mapa_shared(tempty_bar(0), 0) : tempty_bar(0);
+        int titer = 0;
+        int buf = 0;
+        for (int v = cluster_id; v < total_tiles; v += num_clusters, titer++) {
+            const int tile = v / T::SPLIT_K, split = v - tile * T::SPLIT_K;
+            int mb, nb;
+            tile_to_mn(tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
+            const int m0 = mb * T::BM + (int)cta_rank * T::BM_CTA;
+            const int n0 = nb * BN;
+            const int acc = titer & 1;
+            const uint32_t acc_phase = (titer >> 1) & 1;
+            // all 128 epilogue threads must take the same decision, or the ones that go on would
+            // wait at a named barrier for the ones that left
+            const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, acc);
+            if (!named_bar_and(2, 128, got)) break;
+            tc_fence_after_sync();
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            const int grow = m0 + row_in_tile;
+
+#pragma unroll 1
+            for (int j = 0; j < BN / 64; j++) {
+                uint32_t stg = 0;
+                if constexpr (T::EPI == EPI_TMA) {
+                    // the store that last read this staging buffer must have finished reading it
+                    if (epi_tid == 0) tma_store_wait_read<1>();
+                    named_bar_sync(1, 128);
+                    stg = stg_base + buf * (T::BM_CTA * 128);
+                }
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + (uint32_t)(j * 64 + h * 32), r);
+                    tmem_ld_wait();
+                    const int col0 = n0 + j * 64 + h * 32;
+                    if constexpr (T::SPLIT_K > 1) {
+                        if (grow < p.M) {
+                            float *dst = p.workspace + ((size_t)split * p.M + grow) * p.N + col0;
+#pragma unroll
+                            for (int c = 0; c < 8; c++)
+                                if (col0 + c * 4 < p.N)
+                                    *reinterpret_cast<uint4 *>(dst + c * 4) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                        }
+                    } else {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            float lo = __uint_as_float(r[2 * i]), hi = __uint_as_float(r[2 * i + 1]);
+                            if constexpr (T::OPK != OPK_BF16) { lo *= p.alpha; hi *= p.alpha; }
+                            pk[i] = pack_bf16x2(lo, hi);
+                        }
+                        if constexpr (T::EPI == EPI_TMA) {
+#pragma unroll
+                            for (int c = 0; c < 4; c++) {
+                                const uint32_t chunk = (uint32_t)((h * 4 + c) ^ (row_in_tile & 7));
+                                st_shared_v4(stg + row_in_tile * 128 + chunk * 16, pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                            }
+                        } else {
+                            if (grow < p.M) {
+                                bf16 *dst = static_cast<bf16 *>(p.Y) + (size_t)grow * p.N + col0;
+#pragma unroll
+                                for (int c = 0; c < 4; c++)
+                                    if (col0 + c * 8 < p.N)
+                                        *reinterpret_cast<uint4 *>(dst + c * 8) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+                            }
+                        }
+                    }
+                }
+                if constexpr (T::EPI == EPI_TMA) {
+                    fence_proxy_async_smem();
+                    named_bar_sync(1, 128);
+                    if (epi_tid == 0) {
+                        tma_store_2d(&tmap_y, stg, n0 + j * 64, m0);
+                        tma_store_commit();
+                    }
+                    buf ^= 1;
+                }
+            }
+            // accumulator buffer drained: hand it back to the MMA issuer
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (CG == 1) mbar_arrive(tempty_bar(acc));
+                else mbar_arrive_cluster(tempty_leader + 8u * acc);
+            }
+        }
+        if constexpr (T::EPI == EPI_TMA) {
+            if (epi_tid == 0) tma_store_wait<0>();
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncwarp();
+    if (*abort_flag) {
+        // give copies and MMAs still in flight time to land before shared memory and TMEM go away
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc<CG>(tmem_base, T::TMEM_COLS);
+    }
+}
+
+// FP32 partial sums -> bf16: Y[i] = bf16(sum_s ws[s][i]), splits added in ascending order
+// (the reference's order, src/bf16_gemm.cuh:839-845).  Eight outputs per thread: two 128-bit
+// loads per split, one 128-bit store; grid-stride over M*N/8 groups.  Pure HBM traffic:
+// (4*SPLIT_K + 2) bytes per output.  The reference's version handles one element per thread
+// with 4-byte loads and 2-byte stores (src/bf16_gemm.cuh:833-846).
+template <int SPLIT_K>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ ws, bf16 *__restrict__ Y, size_t mn, float alpha)
+{
+    const size_t groups = mn / 8;
+    for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += (size_t)gridDim.x * blockDim.x) {
+        const float4 *src = reinterpret_cast<const float4 *>(ws + g * 8);
+        float4 a = __ldcs(src), b = __ldcs(src + 1);
+#pragma unroll
+        for (int s = 1; s < SPLIT_K; s++) {
+            const float4 *ps = reinterpret_cast<const float4 *>(ws + (size_t)s * mn + g * 8);
+            float4 c = __ldcs(ps), d = __ldcs(ps + 1);
+            a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+            b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
+        }
+        uint4 o;
+        o.x = pack_bf16x2(a.x * alpha, a.y * alpha);
+        o.y = pack_bf16x2(a.z * alpha, a.w * alpha);
+        o.z = pack_bf16x2(b.x * alpha, b.y * alpha);
+        o.w = pack_bf16x2(b.z * alpha, b.w * alpha);
+        *reinterpret_cast<uint4 *>(Y + g * 8) = o;
+    }
+}
+
+// ---------------------------------------------------------------------------------- host side
+template <class T>
+struct UmmaGemmLauncher {
+    static bool can_run(int M, int N, int K)
+    {
+        if (M <= 0 || N <= 0 || K <= 0) return false;
+        if ((K * T::ELEM_BYTES) % 16 != 0 || N % 8 != 0) return false;   // 16-byte row pitches
+        if (T::SPLIT_K > 1) {
+            int kb = (K + T::BK - 1) / T::BK;
+            if (K % T::BK != 0 || kb % T::SPLIT_K != 0) return false;     // equal, non-empty K slices
+        }
+        return true;
+    }
+
+    static size_t workspace_bytes(int M, int N, int K)
+    {
+        (void)K;
+        return T::SPLIT_K > 1 ? (size_t)T::SPLIT_K * M * N * sizeof(float) : 0;
+    }
+
+    // persistent grid: as many CTAs (CTA pairs) as can be resident at once, capped by the
+    // tile count and by `sm_limit`
+    static int grid_size(const DeviceInfo &dev, int total_tiles, int sm_limit, int *out)
+    {
+        static int max_clusters[MAX_DEVICES] = {0};
+        int devid = 0;
+        SM100_CUDA_TRY(cudaGetDevice(&devid));
+        int sms = dev.sm_count;
+        if (T::CG == 2) {
+            if (max_clusters[devid] == 0) {
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(dev.sm_count - dev.sm_count % 2);
+                cfg.blockDim = dim3(T::THREADS);
+                cfg.dynamicSmemBytes = T::SMEM_ALLOC;
+                cudaLaunchAttribute attr;
+                attr.id = cudaLaunchAttributeClusterDimension;
+                attr.val.clusterDim.x = 2;
+                attr.val.clusterDim.y = 1;
+                attr.val.clusterDim.z = 1;
+                cfg.attrs = &attr;
+                cfg.numAttrs = 1;
+                int n = 0;
+                SM100_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, umma_gemm_kernel<T>, &cfg));
+                if (n <= 0) return set_error(GEMM_ERR_CUDA, "no CTA pair of this configuration fits on the device");
+                max_clusters[devid] = n;
+            }
+            sms = 2 * max_clusters[devid];
+            if (sms > dev.sm_count) sms = dev.sm_count - dev.sm_count % 2;
+        }
+        if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
+        int units = sms / T::CG;
+        if (units < 1) units = 1;
+        if (units > total_tiles) units = total_tiles;
+        *out = units * T::CG;
+        return GEMM_OK;
+    }
+
+    static int run(int M, int N, int K, const void *X, const void *W, void *Y, float *workspace, size_t workspace_bytes_given,
+                   float alpha, int sm_limit, cudaStream_t stream)
+    {
+        if (!can_run(M, N, K)) return set_error(GEMM_ERR_SHAPE, "shape %dx%dx%d not supported by this configuration", M, N, K);
+        if (!X || !W || !Y) return set_error(GEMM_ERR_ARG, "null operand pointer");
+        if (T::SPLIT_K > 1) {
+            if (!workspace) return set_error(GEMM_ERR_WORKSPACE, "split-K configuration needs a workspace");
+            if (workspace_bytes_given != 0 && workspace_bytes_given < workspace_bytes(M, N, K))
+                return set_error(GEMM_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes_given, workspace_bytes(M, N, K));
+            if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return set_error(GEMM_ERR_ARG, "workspace must be 16-byte aligned");
+        }
+        DeviceInfo *dev = nullptr;
+        int rc = device_info(&dev);
+        if (rc != GEMM_OK) return rc;
+        if (T::SMEM_ALLOC > dev->max_smem_optin)
+            return set_error(GEMM_ERR_CUDA, "configuration needs %d bytes of shared memory, device allows %d", T::SMEM_ALLOC, dev->max_smem_optin);
+
+        static bool attr_set[MAX_DEVICES] = {false};
+        int devid = 0;
+        SM100_CUDA_TRY(cudaGetDevice(&devid));
+        if (!attr_set[devid]) {
+            SM100_CUDA_TRY(cudaFuncSetAttribute(umma_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_ALLOC));
+            attr_set[devid] = true;
+        }
+
+        const CUtensorMapDataType dt = (T::OPK == OPK_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+        CUtensorMap tx, tw, ty;
+        rc = make_tmap_2d(&tx, dt, X, (uint64_t)K, (uint64_t)M, (uint64_t)K * T::ELEM_BYTES, T::BK, T::BM_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != GEMM_OK) return rc;
+        rc = make_tmap_2d(&tw, dt, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * T::ELEM_BYTES, T::BK, T::BN_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != GEMM_OK) return rc;
+        if (T::EPI == EPI_TMA) {
+            rc = make_tmap_2d(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, Y, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, T::OUT_CHUNK, T::BM_CTA,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc != GEMM_OK) return rc;
+        } else {
+            ty = tx;
+        }
+
+        GemmParams p;
+        p.M = M; p.N = N; p.K = K;
+        p.num_m_blocks = (M + T::BM - 1) / T::BM;
+        p.num_n_blocks = (N + T::BN - 1) / T::BN;
+        p.num_k_blocks = ((K + T::BK - 1) / T::BK) / T::SPLIT_K;
+        p.group_n = (T::BN >= 256) ? 8 : 16;
+        p.Y = Y;
+        p.workspace = workspace;
+        p.alpha = alpha;
+        p.status = dev->status;
+        const int total_tiles = p.num_m_blocks * p.num_n_blocks * T::SPLIT_K;
+        int grid = 0;
+        rc = grid_size(*dev, total_tiles, sm_limit, &grid);
+        if (rc != GEMM_OK) return rc;
+
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(T::THREADS);
+        cfg.dynamicSmemBytes = T::SMEM_ALLOC;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = T::CG;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        SM100_CUDA_TRY(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T>, tx, tw, ty, p));
+
+        if (T::SPLIT_K > 1) {
+            const size_t mn = (size_t)M * N;
+            size_t blocks = (mn / 8 + 255) / 256;
+            const size_t cap = (size_t)dev->sm_count * 8;
+            if (blocks > cap) blocks = cap;
+            splitk_reduce_kernel<T::SPLIT_K><<<(unsigned)blocks, 256, 0, stream>>>(workspace, static_cast<bf16 *>(Y), mn, alpha);
+            SM100_CUDA_TRY(cudaGetLastError());
+        }
+        return GEMM_OK;
+    }
+};
+
+}  // namespace sm100
+
+// The reference's two entry-point class templates (src/bf16_gemm.cuh:193 and :549), kept by
+// name with a static run() of the same argument order; the template parameters are the
+// sm_100 configuration space (tile rows are 128 x CTA_GROUP, BK is fixed by the 128-byte
+// swizzle span).  run() returns a GEMM_* status instead of exiting or throwing.
+template <int BM, int BN, int BK, int NUM_STAGES, int CTA_GROUP = 1, int EPI = sm100::EPI_TMA>
+struct BF16GemmMMA {
+    using Traits = sm100::UmmaGemmTraits<sm100::OPK_BF16, BN, NUM_STAGES, CTA_GROUP, 1, EPI>;
+    static_assert(BM == Traits::BM && BK == Traits::BK, "BM must be 128*CTA_GROUP and BK 64 for bf16");
+    static int run(int M, int N, int K, const bf16 *X, const bf16 *W, bf16 *Y, cudaStream_t stream, int sm_limit = 0)
+    {
+        return sm100::UmmaGemmLauncher<Traits>::run(M, N, K, X, W, Y, nullptr, 0, 1.0f, sm_limit, stream);
+    }
+};
+
+template <int BM, int BN, int BK, int NUM_STAGES, int CTA_GROUP, int SPLIT_K>
+struct BF16GemmMMASplitK {
+    using Traits = sm100::UmmaGemmTraits<sm100::OPK_BF16, BN, NUM_STAGES, CTA_GROUP, SPLIT_K, sm100::EPI_DIRECT>;
+    static_assert(BM == Traits::BM && BK == Traits::BK, "BM must be 128*CTA_GROUP and BK 64 for bf16");
+    // workspace: >= SPLIT_K*M*N floats, caller-owned, need not be zeroed (as src/bf16_gemm.cuh:601)
+    static int run(int M, int N, int K, const bf16 *X, const bf16 *W, bf16 *Y, float *workspace, cudaStream_t stream,
+                   size_t workspace_bytes = 0, int sm_limit = 0)
+    {
+        return sm100::UmmaGemmLauncher<Traits>::run(M, N, K, X, W, Y, workspace, workspace_bytes, 1.0f, sm_limit, stream);
+    }
+};

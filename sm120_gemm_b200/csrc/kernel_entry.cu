@@ -1,0 +1,72 @@
+// One kernel plugin: compiled once per configuration with the configuration given as -D
+// macros, it exports the C ABI declared in include/sm100_gemm.h.
+//
+// Same role as the reference's src/kernel_entry.cu.in:5-27 (a CMake-configured template with
+// eight @VAR@ constants and one exported gemm_run); here the build passes
+//   -DGEMM_DT=<0..4> -DGEMM_BN=<64|128|192|256> -DGEMM_STAGES=<n> -DGEMM_CG=<1|2>
+//   -DGEMM_SK=<split-K> -DGEMM_AB=<0|1 operand swap> -DGEMM_EPI=<0|1>
+#include "bf16_gemm.cuh"
+
+#ifndef GEMM_DT
+#error "configuration macros missing: build through sm120_gemm_b200/build.py"
+#endif
+
+namespace {
+
+constexpr int DT = GEMM_DT;
+constexpr int BN = GEMM_BN;
+constexpr int STAGES = GEMM_STAGES;
+constexpr int CG = GEMM_CG;
+constexpr int SK = GEMM_SK;
+constexpr int AB = GEMM_AB;
+constexpr int EPI = GEMM_EPI;
+constexpr int BM = 128 * CG;
+
+static_assert(DT == GEMM_DT_BF16 || DT == GEMM_DT_FP8, "this entry file builds the dense bf16 / fp8 kernels");
+static_assert(AB == 0, "operand swap is not part of the dense kernel");
+
+using Traits = sm100::UmmaGemmTraits<DT == GEMM_DT_BF16 ? sm100::OPK_BF16 : sm100::OPK_E4M3, BN, STAGES, CG, SK, EPI>;
+using Launcher = sm100::UmmaGemmLauncher<Traits>;
+
+#define GEMM_STR2(x) #x
+#define GEMM_STR(x) GEMM_STR2(x)
+const char *const kConfigName = GEMM_STR(GEMM_NAME);
+
+}  // namespace
+
+extern "C" {
+
+void gemm_run(int M, int N, int K, const void *X, const void *W, void *Y, float *workspace, gemm_stream_t stream)
+{
+    sm100::clear_error();
+    if (DT != GEMM_DT_BF16) {
+        sm100::set_error(GEMM_ERR_ARG, "gemm_run takes bf16 operands; %s needs gemm_run_ex", kConfigName);
+        return;
+    }
+    Launcher::run(M, N, K, X, W, Y, workspace, 0, 1.0f, 0, stream);
+}
+
+int gemm_run_ex(const GemmArgs *a)
+{
+    sm100::clear_error();
+    if (!a || a->struct_size != sizeof(GemmArgs)) return sm100::set_error(GEMM_ERR_ARG, "GemmArgs is null or has the wrong struct_size");
+    if ((int)a->dtype != DT) return sm100::set_error(GEMM_ERR_ARG, "dtype %u does not match plugin %s", a->dtype, kConfigName);
+    const float alpha = (DT == GEMM_DT_FP8) ? a->x_scale_f * a->w_scale_f : 1.0f;
+    return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, static_cast<float *>(a->workspace), a->workspace_bytes, alpha,
+                         a->sm_limit, a->stream);
+}
+
+const char *gemm_config_name(void) { return kConfigName; }
+size_t gemm_workspace_bytes(int M, int N, int K) { return Launcher::workspace_bytes(M, N, K); }
+int gemm_can_run(int M, int N, int K) { return Launcher::can_run(M, N, K) ? 1 : 0; }
+size_t gemm_smem_bytes(void) { return Traits::SMEM_ALLOC; }
+int gemm_last_error(void) { return sm100::error_state().code; }
+const char *gemm_last_error_message(void) { return sm100::error_state().msg; }
+
+int gemm_check_status(void)
+{
+    uint32_t st[4];
+    return sm100::read_device_status(st);
+}
+
+}  // extern "C"

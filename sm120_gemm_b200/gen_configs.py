@@ -1,0 +1,129 @@
+"""Enumerates the kernel configurations to build, one shared library each.
+
+Same job as the reference's scripts/gen_configs.py:7-50 (which enumerates
+BM,BN in {64,128} x stages x consumer warpgroups x warp tilings x split-K under a
+shared-memory cap for the mma.sync kernel), re-derived for the tcgen05 design:
+
+  dt       bf16 | fp8 | mxfp8 | w4a16 | w4a4
+  bm       128 (one CTA) or 256 (CTA pair, cta_group::2); always 128*cg
+  bn       64 | 128 | 192 | 256      (UMMA N; two FP32 accumulator buffers need 2*bn <= 512 TMEM columns)
+  bk       one 128-byte swizzle span of K per stage: 64 bf16, 128 fp8, 256 fp4 elements
+  s        TMA ring stages, bounded by the 227 KB of shared memory one CTA may use
+  cg       CTA group (1 | 2)
+  sk       split-K factor (FP32 partials + reduce kernel)
+  ab       operand swap for small M (W rows on the 128 accumulator lanes)
+  e        epilogue: 0 = registers -> global, 1 = swizzled shared memory -> TMA store
+
+Name:  <dt>_bm<bm>_bn<bn>_bk<bk>_s<s>_cg<cg>_sk<sk>_ab<ab>_e<e>
+
+The warp-tiling fields of the reference's names (cwg, wm, wn) have no meaning for a
+single-thread-issued MMA and are gone.
+"""
+from __future__ import annotations
+
+import argparse
+import re
+from dataclasses import dataclass
+
+MAX_SMEM = 232448  # 227 KB: cudaDevAttrMaxSharedMemoryPerBlockOptin on sm_100
+DT_IDS = {"bf16": 0, "fp8": 1, "mxfp8": 2, "w4a16": 3, "w4a4": 4}
+ELEM_BITS = {"bf16": 16, "fp8": 8, "mxfp8": 8, "w4a16": 16, "w4a4": 4}
+
+_NAME_RE = re.compile(r"^(bf16|fp8|mxfp8|w4a16|w4a4)_bm(\d+)_bn(\d+)_bk(\d+)_s(\d+)_cg(\d+)_sk(\d+)_ab(\d+)_e(\d+)$")
+
+
+@dataclass(frozen=True)
+class GemmConfig:
+    """Mirror of the reference's GemmConfig (src/gemm_config.h:24-55) for the new space."""
+
+    dt: str
+    bm: int
+    bn: int
+    bk: int
+    num_stages: int
+    cg: int
+    split_k: int
+    swap_ab: int
+    epi: int
+
+    def name(self) -> str:
+        return (f"{self.dt}_bm{self.bm}_bn{self.bn}_bk{self.bk}_s{self.num_stages}_cg{self.cg}"
+                f"_sk{self.split_k}_ab{self.swap_ab}_e{self.epi}")
+
+    @staticmethod
+    def parse(s: str):
+        m = _NAME_RE.match(s)
+        if not m:
+            return None
+        g = m.groups()
+        return GemmConfig(g[0], *(int(v) for v in g[1:]))
+
+    def smem_bytes(self) -> int:
+        """Dynamic shared memory of the dense kernel; must equal UmmaGemmTraits::SMEM_ALLOC."""
+        a = 128 * 128
+        b = (self.bn // self.cg) * 128
+        epi = 0 if self.split_k > 1 else self.epi
+        staging = 2 * 128 * 64 * 2 if epi == 1 else 0
+        barriers = (2 * self.num_stages + 4) * 8 + 16
+        return self.num_stages * (a + b) + staging + barriers + 1024
+
+    def is_valid_for(self, M: int, N: int, K: int) -> bool:
+        """The plugin's own gemm_can_run, restated (reference: src/gemm_config.h:34-38)."""
+        if M <= 0 or N <= 0 or K <= 0:
+            return False
+        if (K * ELEM_BITS[self.dt]) % 128 != 0 or N % 8 != 0:
+            return False
+        if self.split_k > 1:
+            if K % self.bk != 0 or (K // self.bk) % self.split_k != 0:
+                return False
+        return True
+
+    def defines(self) -> list[str]:
+        return [f"-DGEMM_DT={DT_IDS[self.dt]}", f"-DGEMM_BN={self.bn}", f"-DGEMM_STAGES={self.num_stages}",
+                f"-DGEMM_CG={self.cg}", f"-DGEMM_SK={self.split_k}", f"-DGEMM_AB={self.swap_ab}",
+                f"-DGEMM_EPI={self.epi}", f"-DGEMM_NAME={self.name()}"]
+
+
+def max_stages(dt: str, bn: int, cg: int, sk: int, epi: int, cap: int = MAX_SMEM) -> int:
+    bk = 128 * 8 // ELEM_BITS[dt]
+    s = 12
+    while s >= 2 and GemmConfig(dt, 128 * cg, bn, bk, s, cg, sk, 0, epi).smem_bytes() > cap:
+        s -= 1
+    return s
+
+
+def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8")) -> list[GemmConfig]:
+    out: list[GemmConfig] = []
+    for dt in dts:
+        if dt not in ("bf16", "fp8"):
+            continue  # the block-scaled and W4A16 kernels have their own generators
+        bk = 128 * 8 // ELEM_BITS[dt]
+        for cg in (1, 2):
+            for bn in (64, 128, 192, 256):
+                for epi in (1, 0):
+                    top = max_stages(dt, bn, cg, 1, epi, max_smem)
+                    stage_opts = sorted({min(top, 8), min(top, 4)}, reverse=True)
+                    if epi == 0:
+                        stage_opts = stage_opts[:1]
+                    for s in stage_opts:
+                        if s >= 2:
+                            out.append(GemmConfig(dt, 128 * cg, bn, bk, s, cg, 1, 0, epi))
+        # split-K: for shapes with too few output tiles to fill 148 SMs (decode, M <= 128)
+        for cg, bn in ((1, 64), (1, 128), (1, 256), (2, 128), (2, 256)):
+            for sk in (2, 4, 7, 8, 16):
+                s = min(max_stages(dt, bn, cg, sk, 0, max_smem), 8)
+                out.append(GemmConfig(dt, 128 * cg, bn, bk, s, cg, sk, 0, 0))
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--max-smem-kb", type=int, default=MAX_SMEM // 1024)
+    ap.add_argument("--dt", default="bf16,fp8")
+    args = ap.parse_args()
+    for c in generate_configs(args.max_smem_kb * 1024, tuple(args.dt.split(","))):
+        print(c.name())
+
+
+if __name__ == "__main__":
+    main()
