@@ -1,0 +1,281 @@
+// Host-side registry, configuration parser, autotune cache and dispatch for the sm_100a
+// kernel plugins.  Header-only C++17; needs only libdl and the C ABI in include/sm100_gemm.h.
+//
+// It keeps the reference's host surface by name so a caller of src/gemm_config.h can switch
+// over: GemmConfig (reference :24-55), LoadedKernel (:58-62), KernelRegistry (:65-120),
+// AutotuneCache (:124-170), dispatch (:173-178).  What changed and why:
+//   * the configuration fields are those of the tcgen05 kernels (data type, CTA group,
+//     operand swap, epilogue kind) instead of warp tilings;
+//   * a plugin answers can_run / workspace_bytes / smem_bytes itself, so the host-side model
+//     cannot drift from the kernel (the reference keeps three copies of the smem formula);
+//   * the cache key carries the data type and the GPU count, the file is replaced atomically,
+//     and old three-field lines are still read as bf16 on one GPU;
+//   * errors come back as status codes; nothing here calls exit().
+#pragma once
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <filesystem>
+#include <fstream>
+#include <map>
+#include <optional>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "../../include/sm100_gemm.h"
+
+namespace sm100 {
+inline const char *const kDtypeNames[] = {"bf16", "fp8", "mxfp8", "w4a16", "w4a4"};
+inline int dtype_from_name(const char *s)
+{
+    for (int i = 0; i < 5; i++)
+        if (std::strcmp(s, kDtypeNames[i]) == 0) return i;
+    return -1;
+}
+inline int elem_bits(int dt) { return dt == GEMM_DT_BF16 || dt == GEMM_DT_W4A16 ? 16 : dt == GEMM_DT_W4A4 ? 4 : 8; }
+}  // namespace sm100
+
+struct GemmConfig {
+    int dt = GEMM_DT_BF16;  // GEMM_DT_*
+    int bm = 128, bn = 128, bk = 64, num_stages = 4;
+    int cg = 1;             // CTA group: 1, or 2 for a CTA pair sharing one 256-row tile
+    int split_k = 1;
+    int swap_ab = 0;        // 1: W rows on the accumulator lanes (small-M shapes)
+    int epi = 1;            // 0: register->global epilogue, 1: shared memory + TMA store
+
+    std::string name() const
+    {
+        char buf[160];
+        std::snprintf(buf, sizeof(buf), "%s_bm%d_bn%d_bk%d_s%d_cg%d_sk%d_ab%d_e%d", sm100::kDtypeNames[dt], bm, bn, bk,
+                      num_stages, cg, split_k, swap_ab, epi);
+        return buf;
+    }
+
+    static std::optional<GemmConfig> parse(const std::string &s)
+    {
+        GemmConfig c;
+        char dt_name[16] = {0};
+        int consumed = 0;
+        int n = std::sscanf(s.c_str(), "%15[a-z0-9]_bm%d_bn%d_bk%d_s%d_cg%d_sk%d_ab%d_e%d%n", dt_name, &c.bm, &c.bn, &c.bk,
+                            &c.num_stages, &c.cg, &c.split_k, &c.swap_ab, &c.epi, &consumed);
+        if (n != 9 || consumed != (int)s.size()) return std::nullopt;
+        c.dt = sm100::dtype_from_name(dt_name);
+        if (c.dt < 0) return std::nullopt;
+        return c;
+    }
+
+    // Shapes the dense kernels accept: 16-byte row pitches; split-K needs equal, whole K slices.
+    // M, N, K need not divide by the tile (TMA zero-fills and clips), unlike the reference.
+    bool is_valid_for(int M, int N, int K) const
+    {
+        if (M <= 0 || N <= 0 || K <= 0) return false;
+        if (((long long)K * sm100::elem_bits(dt)) % 128 != 0 || N % 8 != 0) return false;
+        if (split_k > 1 && (K % bk != 0 || (K / bk) % split_k != 0)) return false;
+        return true;
+    }
+
+    // Dynamic shared memory of the dense kernel (must equal UmmaGemmTraits::SMEM_ALLOC;
+    // a plugin reports the exact figure through gemm_smem_bytes()).
+    size_t smem_bytes() const
+    {
+        const size_t a = 128 * 128, b = (size_t)(bn / cg) * 128;
+        const size_t staging = (split_k == 1 && epi == 1) ? 2 * 128 * 64 * 2 : 0;
+        const size_t barriers = (2 * (size_t)num_stages + 4) * 8 + 16;
+        return num_stages * (a + b) + staging + barriers + 1024;
+    }
+};
+
+// Function-pointer types of the plugin ABI.
+using GemmKernelFn = void (*)(int M, int N, int K, const void *X, const void *W, void *Y, float *workspace, gemm_stream_t stream);
+using GemmKernelExFn = int (*)(const GemmArgs *);
+
+struct LoadedKernel {
+    GemmConfig config;
+    GemmKernelFn fn = nullptr;       // gemm_run
+    GemmKernelExFn fn_ex = nullptr;  // gemm_run_ex
+    size_t (*workspace_bytes)(int, int, int) = nullptr;
+    int (*can_run)(int, int, int) = nullptr;
+    size_t (*smem_bytes)() = nullptr;
+    int (*last_error)() = nullptr;
+    const char *(*last_error_message)() = nullptr;
+    int (*check_status)() = nullptr;
+    void *dl_handle = nullptr;
+};
+
+struct KernelRegistry {
+    std::vector<LoadedKernel> kernels;
+    bool quiet = false;
+
+    KernelRegistry() = default;
+    KernelRegistry(const KernelRegistry &) = delete;
+    KernelRegistry &operator=(const KernelRegistry &) = delete;
+
+    // Loads every libgemm_<config>.so of `dir`; files that do not parse, do not load or miss
+    // a symbol are reported and skipped.  Returns whether anything was loaded.
+    bool load_dir(const std::string &dir, int only_dt = -1)
+    {
+        namespace fs = std::filesystem;
+        std::error_code ec;
+        if (!fs::is_directory(dir, ec)) {
+            std::fprintf(stderr, "KernelRegistry: not a directory: %s\n", dir.c_str());
+            return false;
+        }
+        std::vector<fs::path> files;
+        for (const auto &e : fs::directory_iterator(dir, ec))
+            if (e.path().extension() == ".so") files.push_back(e.path());
+        std::sort(files.begin(), files.end());
+        static const std::string prefix = "libgemm_";
+        for (const auto &path : files) {
+            const std::string stem = path.stem().string();
+            if (stem.compare(0, prefix.size(), prefix) != 0) continue;
+            auto cfg = GemmConfig::parse(stem.substr(prefix.size()));
+            if (!cfg) {
+                std::fprintf(stderr, "KernelRegistry: cannot parse config from %s\n", stem.c_str());
+                continue;
+            }
+            if (only_dt >= 0 && cfg->dt != only_dt) continue;
+            void *h = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL);
+            if (!h) {
+                std::fprintf(stderr, "KernelRegistry: dlopen failed for %s: %s\n", path.c_str(), dlerror());
+                continue;
+            }
+            LoadedKernel k;
+            k.config = *cfg;
+            k.dl_handle = h;
+            bool ok = true;
+            auto sym = [&](const char *name) {
+                void *p = dlsym(h, name);
+                if (!p) {
+                    std::fprintf(stderr, "KernelRegistry: dlsym(%s) failed for %s\n", name, path.c_str());
+                    ok = false;
+                }
+                return p;
+            };
+            k.fn = reinterpret_cast<GemmKernelFn>(sym("gemm_run"));
+            k.fn_ex = reinterpret_cast<GemmKernelExFn>(sym("gemm_run_ex"));
+            k.workspace_bytes = reinterpret_cast<size_t (*)(int, int, int)>(sym("gemm_workspace_bytes"));
+            k.can_run = reinterpret_cast<int (*)(int, int, int)>(sym("gemm_can_run"));
+            k.smem_bytes = reinterpret_cast<size_t (*)()>(sym("gemm_smem_bytes"));
+            k.last_error = reinterpret_cast<int (*)()>(sym("gemm_last_error"));
+            k.last_error_message = reinterpret_cast<const char *(*)()>(sym("gemm_last_error_message"));
+            k.check_status = reinterpret_cast<int (*)()>(sym("gemm_check_status"));
+            auto name_fn = reinterpret_cast<const char *(*)()>(sym("gemm_config_name"));
+            if (ok && cfg->name() != name_fn()) {
+                std::fprintf(stderr, "KernelRegistry: %s was built as %s\n", stem.c_str(), name_fn());
+                ok = false;
+            }
+            if (!ok) {
+                dlclose(h);
+                continue;
+            }
+            kernels.push_back(k);
+        }
+        if (!quiet) std::printf("KernelRegistry: loaded %zu kernels from %s\n", kernels.size(), dir.c_str());
+        return !kernels.empty();
+    }
+
+    std::vector<const LoadedKernel *> get_valid(int M, int N, int K, size_t max_smem = 0, int dt = GEMM_DT_BF16) const
+    {
+        std::vector<const LoadedKernel *> out;
+        for (const auto &k : kernels) {
+            if (k.config.dt != dt || !k.can_run(M, N, K)) continue;
+            if (max_smem > 0 && k.smem_bytes() > max_smem) continue;
+            out.push_back(&k);
+        }
+        return out;
+    }
+
+    const LoadedKernel *find(const std::string &name) const
+    {
+        for (const auto &k : kernels)
+            if (k.config.name() == name) return &k;
+        return nullptr;
+    }
+
+    ~KernelRegistry()
+    {
+        for (auto &k : kernels)
+            if (k.dl_handle) dlclose(k.dl_handle);
+    }
+};
+
+// Text file, one result per line:  dt,gpus,M,N,K config_name time_ms   ('#' starts a comment).
+struct AutotuneCache {
+    using Key = std::tuple<int, int, int, int, int>;  // dt, gpus, M, N, K
+    struct Entry {
+        GemmConfig config;
+        double time_ms;
+    };
+    std::map<Key, Entry> entries;
+    bool quiet = false;
+
+    bool load(const std::string &path)
+    {
+        std::ifstream f(path);
+        if (!f.is_open()) return false;
+        std::string line;
+        size_t skipped = 0;
+        while (std::getline(f, line)) {
+            if (line.empty() || line[0] == '#') continue;
+            char key[96], name[160];
+            double ms = 0;
+            if (std::sscanf(line.c_str(), "%95s %159s %lf", key, name, &ms) != 3) { skipped++; continue; }
+            auto cfg = GemmConfig::parse(name);
+            char dt_name[16];
+            int g, M, N, K, used = 0;
+            Key k;
+            if (std::sscanf(key, "%15[a-z0-9],%d,%d,%d,%d%n", dt_name, &g, &M, &N, &K, &used) == 5 && key[used] == 0 &&
+                sm100::dtype_from_name(dt_name) >= 0)
+                k = {sm100::dtype_from_name(dt_name), g, M, N, K};
+            else if (std::sscanf(key, "%d,%d,%d%n", &M, &N, &K, &used) == 3 && key[used] == 0)
+                k = {GEMM_DT_BF16, 1, M, N, K};   // the reference's key format
+            else { skipped++; continue; }
+            if (!cfg) { skipped++; continue; }
+            entries[k] = {*cfg, ms};
+        }
+        if (!quiet) std::printf("AutotuneCache: loaded %zu entries from %s (%zu lines skipped)\n", entries.size(), path.c_str(), skipped);
+        return true;
+    }
+
+    bool save(const std::string &path) const
+    {
+        const std::string tmp = path + ".tmp";
+        {
+            std::ofstream f(tmp);
+            if (!f.is_open()) return false;
+            f << "# Autotune cache -- dt,gpus,M,N,K config_name time_ms\n";
+            for (const auto &[key, e] : entries) {
+                const auto &[dt, g, M, N, K] = key;
+                f << sm100::kDtypeNames[dt] << ',' << g << ',' << M << ',' << N << ',' << K << ' ' << e.config.name() << ' ' << e.time_ms << '\n';
+            }
+        }
+        std::error_code ec;
+        std::filesystem::rename(tmp, path, ec);
+        if (!quiet) std::printf("AutotuneCache: saved %zu entries to %s\n", entries.size(), path.c_str());
+        return !ec;
+    }
+
+    std::optional<Entry> lookup(int M, int N, int K, int dt = GEMM_DT_BF16, int gpus = 1) const
+    {
+        auto it = entries.find({dt, gpus, M, N, K});
+        if (it == entries.end()) return std::nullopt;
+        return it->second;
+    }
+
+    void store(int M, int N, int K, const GemmConfig &config, double time_ms, int dt = GEMM_DT_BF16, int gpus = 1)
+    {
+        entries[{dt, gpus, M, N, K}] = {config, time_ms};
+    }
+};
+
+// One indirect call into the plugin, BF16 operands (the reference's dispatch).  Returns the
+// plugin's error code for the call (GEMM_OK when the launch was queued).
+inline int dispatch(const LoadedKernel &kernel, int M, int N, int K, const void *X, const void *W, void *Y, float *workspace,
+                    gemm_stream_t stream)
+{
+    kernel.fn(M, N, K, X, W, Y, workspace, stream);
+    return kernel.last_error();
+}
