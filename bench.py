@@ -1,0 +1,280 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: BF16 Y = X * W^T, M = N = K = 16384 (BASELINE config 3), FP32
+accumulate, on N GPUs of one node.  At N > 1 the weight rows are sharded (N/g per rank) and
+one NCCL all-gather collects the bf16 column blocks of Y; total work is fixed (strong scaling).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line on rank 0.  `value` is device-timed TFLOPS with inputs resident in HBM;
+`e2e` is the same metric through the plugin C ABI with HOST buffers (pinned host -> device
+copies of X and W and the device -> host copy of Y inside the timed region).  The reference
+arm times the CPU restatement of the reference's FP32 check loop (it has no CPU code of its
+own) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M = N = K = 16384
+WORKLOAD = "bf16 gemm Y=X*W^T M=N=K=16384, X,W~N(0,1) seed 2, fp32 accumulate, bf16 out (BASELINE config 3)"
+DEFAULT_KERNEL = "bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel at this workload,
+# from the ncu capture summarised under profiles/ (None until captured)
+NCU_TRAFFIC_BYTES = None
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+                "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.samples, self.reasons, self.max_mhz = index, False, [], set(), None
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap", nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                     nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonHwPowerBrakeSlowdown: "hw_power_brake_slowdown"}
+            while not self.stop_flag:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+                time.sleep(0.004)
+        except Exception as e:  # NVML missing: report it instead of inventing numbers
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def result(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def cpu_baseline(seconds_target: float = 12.0):
+    """Times the CPU oracle (restatement of the reference's FP32 loop, src/bench.cu:77-84) on a
+    row slab of the same 16384^3 workload, all host threads."""
+    import numpy as np
+
+    from oracle import oracle as o
+
+    rng = np.random.default_rng(2)
+    W = o.f32_to_bf16_bits(rng.standard_normal((N, K), dtype=np.float32))
+    rows = 32
+    X = o.f32_to_bf16_bits(rng.standard_normal((rows, K), dtype=np.float32))
+    t0 = time.perf_counter(); o.gemm_bf16(X, W); t1 = time.perf_counter() - t0   # includes the bf16->fp32 conversion of W
+    t0 = time.perf_counter(); o.gemm_bf16(X, W); t1 = min(t1, time.perf_counter() - t0)
+    # grow the slab so the timed pass lasts about seconds_target
+    rows2 = int(min(4096, max(64, rows * seconds_target / max(t1, 1e-3) * 0.5)))
+    X = o.f32_to_bf16_bits(rng.standard_normal((rows2, K), dtype=np.float32))
+    t0 = time.perf_counter(); o.gemm_bf16(X, W); dt = time.perf_counter() - t0
+    tflops = 2.0 * rows2 * N * K / dt / 1e12
+    return {"value": tflops, "unit": "TFLOPS", "cores": o.num_threads(), "kind": "port",
+            "sample": f"{rows2} of {M} rows of Y (all {N} columns, K={K}), one timed pass of {dt:.1f} s after a warm pass"}, W
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+
+    from oracle import oracle as o
+
+    base, W = cpu_baseline(4.0)
+    rng = np.random.default_rng(2)
+    rows = 256
+    X = o.f32_to_bf16_bits(rng.standard_normal((rows, K), dtype=np.float32))
+    for _ in range(min(args.warmup, 1)):
+        o.gemm_bf16(X, W)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        o.gemm_bf16(X, W)
+    dt = time.perf_counter() - t0
+    tflops = 2.0 * rows * N * K * args.steps / dt / 1e12
+    sample = f"each step = {rows} of {M} rows of Y on the host cores (CPU port of the reference's FP32 loop; the reference has no CPU implementation)"
+    print(json.dumps({
+        "impl": "reference", "metric": "gemm_tflops", "value": tflops, "unit": "TFLOPS", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOPS", "cores": o.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel", default=None, help="plugin configuration name (default: autotune cache, then built-in choice)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    import sm120_gemm_b200 as g
+    from sm120_gemm_b200.shard import NShardedGemm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        sys.exit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    if not torch.cuda.is_available():
+        sys.exit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    reg = g.KernelRegistry()
+    if not reg.load_dir(g.KERNEL_DIR, dt="bf16"):
+        sys.exit("no kernel plugins found: run python -c 'import __graft_entry__ as e; e.build()'")
+    cache = g.AutotuneCache()
+    cache.load(os.path.join(ROOT, "sm120_gemm_b200", "autotune_cache.txt"))
+    name = args.kernel
+    if name is None:
+        hit = cache.lookup(M, N // world, K, "bf16", 1)
+        name = hit[0].name() if hit else DEFAULT_KERNEL
+    kern = reg.find(name)
+    if kern is None:
+        sys.exit(f"plugin {name} is not built")
+
+    plan_rows = N // world
+    gen = torch.Generator(device=dev); gen.manual_seed(2)
+    X = torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16)
+    Wfull_seed = torch.Generator(device=dev); Wfull_seed.manual_seed(1002)
+    # every rank draws the same W stream and keeps its own rows (W never crosses GPUs)
+    W = torch.empty((plan_rows, K), dtype=torch.bfloat16, device=dev)
+    chunk = 2048
+    for r0 in range(0, N, chunk):
+        blk = torch.randn((chunk, K), device=dev, generator=Wfull_seed).to(torch.bfloat16)
+        lo, hi = max(r0, rank * plan_rows), min(r0 + chunk, (rank + 1) * plan_rows)
+        if lo < hi:
+            W[lo - rank * plan_rows:hi - rank * plan_rows] = blk[lo - r0:hi - r0]
+    del blk
+    Y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    op = NShardedGemm(kern, M, N, K, rank, world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    launches_per_step = 0
+    for _ in range(args.warmup):
+        launches_per_step = op.run(X, W, Y)
+    if kern.config.split_k > 1:
+        launches_per_step += 1
+    barrier()
+    kern.check_status()
+
+    sampler = ClockSampler(local_rank); sampler.start()
+    time.sleep(0.02)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        starts[i].record()
+        op.run(X, W, Y)
+        ends[i].record()
+    e1.record()
+    barrier()
+    sampler.stop_flag = True; sampler.join(timeout=2)
+    total_ms = e0.elapsed_time(e1)
+    per_step = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    kern.check_status()
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+
+    # ---- end to end: host buffers, copies inside the timed region (plugin C ABI in the middle)
+    Xh = torch.empty((M, K), dtype=torch.bfloat16).pin_memory(); Xh.copy_(X)
+    Wh = torch.empty((plan_rows, K), dtype=torch.bfloat16).pin_memory(); Wh.copy_(W)
+    Yh = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_step():
+        X.copy_(Xh, non_blocking=True)
+        W.copy_(Wh, non_blocking=True)
+        op.run(X, W, Y)
+        Yh.copy_(Y, non_blocking=True)
+
+    e2e_step(); barrier()
+    f0 = torch.cuda.Event(enable_timing=True); f1 = torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+
+    if rank == 0:
+        flops = 2.0 * M * N * K
+        peaks = load_peaks()
+        value = flops * args.steps / (total_ms * 1e-3) / 1e12
+        # roofline of the dominant kernel (the tcgen05 GEMM): per-launch time = the step's event
+        # time at N=1 (one kernel per step); at N>1 the step also holds the all-gather, so the
+        # kernel-level figure is only reported for the single-GPU run
+        launch_ms = sum(per_step) / len(per_step)
+        kflops = flops / world
+        achieved = kflops / (launch_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved if world == 1 else None, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["bf16_tflops"] if world == 1 else None, "traffic": NCU_TRAFFIC_BYTES,
+                    "peak_source": f"{peaks['source']} (cuBLAS bf16 burst; sustained {peaks['bf16_tflops_sustained']})",
+                    "kernel": f"umma_gemm_kernel<{kern.config.name()}>", "flops_per_launch": kflops, "avg_launch_ms": launch_ms}
+        out = {
+            "metric": "gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "kernel": kern.config.name(), "l2": "inputs larger than L2 (X, W, Y = 1.5 GiB vs 126 MB L2)",
+                       "parallelism": "single GPU" if world == 1 else f"N-sharded x{world}: {plan_rows} weight rows per rank + NCCL all-gather + interleave"},
+            "roofline": roofline,
+            "e2e": {"value": flops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+                    "h2d_bytes_per_step": (M * K + plan_rows * K) * 2, "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": sampler.result(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"], _ = cpu_baseline()
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

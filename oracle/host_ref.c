@@ -70,80 +70,102 @@ void oracle_f32_to_bf16(const float *src, uint16_t *dst, size_t n)
         dst[i] = f32_to_bf16(src[i]);
 }
 
-/* one dot product, strict k-ascending FP32 order: reference src/bench.cu:77-84 */
-static float dot_strict(const float *x, const float *w, int K)
-{
-    volatile float acc = 0.0f; /* volatile: no reassociation, no vectorisation */
-    for (int k = 0; k < K; k++) {
-        float p = x[k] * w[k];
-        acc = acc + p;
+/*
+ * Fast mode building block: a 4-row x 4-column block of dot products over the full K, sixteen
+ * FP32 accumulators, every operand element converted to FP32 where it is used (as the
+ * reference loop does, src/bench.cu:79-81).  Additions inside one dot product are reordered
+ * across SIMD lanes only.
+ */
+#define DOT4(T, CVT)                                                                               \
+    static void dot_block_##T(const T *const x[4], const T *const w[4], int K, float out[4][4])    \
+    {                                                                                              \
+        float a00 = 0, a01 = 0, a02 = 0, a03 = 0, a10 = 0, a11 = 0, a12 = 0, a13 = 0;              \
+        float a20 = 0, a21 = 0, a22 = 0, a23 = 0, a30 = 0, a31 = 0, a32 = 0, a33 = 0;              \
+        const T *x0 = x[0], *x1 = x[1], *x2 = x[2], *x3 = x[3];                                    \
+        const T *w0 = w[0], *w1 = w[1], *w2 = w[2], *w3 = w[3];                                    \
+        _Pragma("omp simd reduction(+ : a00, a01, a02, a03, a10, a11, a12, a13, a20, a21, a22, a23, a30, a31, a32, a33)") \
+        for (int k = 0; k < K; k++) {                                                              \
+            float p0 = CVT(x0[k]), p1 = CVT(x1[k]), p2 = CVT(x2[k]), p3 = CVT(x3[k]);              \
+            float q0 = CVT(w0[k]), q1 = CVT(w1[k]), q2 = CVT(w2[k]), q3 = CVT(w3[k]);              \
+            a00 += p0 * q0; a01 += p0 * q1; a02 += p0 * q2; a03 += p0 * q3;                        \
+            a10 += p1 * q0; a11 += p1 * q1; a12 += p1 * q2; a13 += p1 * q3;                        \
+            a20 += p2 * q0; a21 += p2 * q1; a22 += p2 * q2; a23 += p2 * q3;                        \
+            a30 += p3 * q0; a31 += p3 * q1; a32 += p3 * q2; a33 += p3 * q3;                        \
+        }                                                                                          \
+        out[0][0] = a00; out[0][1] = a01; out[0][2] = a02; out[0][3] = a03;                        \
+        out[1][0] = a10; out[1][1] = a11; out[1][2] = a12; out[1][3] = a13;                        \
+        out[2][0] = a20; out[2][1] = a21; out[2][2] = a22; out[2][3] = a23;                        \
+        out[3][0] = a30; out[3][1] = a31; out[3][2] = a32; out[3][3] = a33;                        \
     }
-    return acc;
-}
+#define CVT_F32(v) (v)
+#define CVT_BF16(v) bf16_to_f32(v)
+typedef uint16_t bf16_t;
+DOT4(float, CVT_F32)
+DOT4(bf16_t, CVT_BF16)
 
 /*
- * Y[rows[i], :] for i < n_rows (rows == NULL means rows 0..n_rows-1), FP32 operands.
- * Fast mode: 4 output columns at a time so each X row segment is reused from
- * registers/L1; additions inside a dot product are reordered across SIMD lanes only.
+ * Shared driver: Y[i, :] = X[rows[i], :] . W^T for i < n_rows (rows == NULL: rows 0..n_rows-1).
+ * Work is cut into (16-row block) x (256-column chunk) tasks so a block of X stays in cache
+ * while W streams past it once per row block.
  */
+#define GEMM_ROWS(NAME, T, DOTFN, CVT)                                                              \
+    static void NAME(int N, int K, const T *X, const T *W, float *Y, const int *rows, int n_rows, int strict) \
+    {                                                                                               \
+        const int RB = 16, CB = 256;                                                                \
+        const int nrb = (n_rows + RB - 1) / RB, ncb = (N + CB - 1) / CB;                            \
+        _Pragma("omp parallel for collapse(2) schedule(dynamic, 1)")                                \
+        for (int rb = 0; rb < nrb; rb++)                                                            \
+            for (int cb = 0; cb < ncb; cb++) {                                                      \
+                const int i1 = (rb + 1) * RB < n_rows ? (rb + 1) * RB : n_rows;                     \
+                const int c1 = (cb + 1) * CB < N ? (cb + 1) * CB : N;                               \
+                for (int c = cb * CB; c < c1; c += 4)                                               \
+                    for (int i = rb * RB; i < i1; i += 4) {                                         \
+                        const T *xp[4], *wp[4];                                                     \
+                        for (int u = 0; u < 4; u++) {                                               \
+                            int ii = i + u < i1 ? i + u : i1 - 1;                                   \
+                            int cc = c + u < c1 ? c + u : c1 - 1;                                   \
+                            xp[u] = X + (size_t)(rows ? rows[ii] : ii) * K;                         \
+                            wp[u] = W + (size_t)cc * K;                                             \
+                        }                                                                           \
+                        float out[4][4];                                                            \
+                        if (strict) {                                                               \
+                            for (int u = 0; u < 4; u++)                                             \
+                                for (int v = 0; v < 4; v++) {                                       \
+                                    volatile float acc = 0.0f; /* k ascending, no reassociation */  \
+                                    for (int k = 0; k < K; k++) {                                   \
+                                        float pr = CVT(xp[u][k]) * CVT(wp[v][k]);                   \
+                                        acc = acc + pr;                                             \
+                                    }                                                               \
+                                    out[u][v] = acc;                                                \
+                                }                                                                   \
+                        } else {                                                                    \
+                            DOTFN(xp, wp, K, out);                                                  \
+                        }                                                                           \
+                        for (int u = 0; u < 4 && i + u < i1; u++)                                   \
+                            for (int v = 0; v < 4 && c + v < c1; v++)                               \
+                                Y[(size_t)(i + u) * N + c + v] = out[u][v];                         \
+                    }                                                                               \
+            }                                                                                       \
+    }
+GEMM_ROWS(gemm_rows_f32, float, dot_block_float, CVT_F32)
+GEMM_ROWS(gemm_rows_bf16, bf16_t, dot_block_bf16_t, CVT_BF16)
+
+/* FP32 operands (the dequantise-then-GEMM oracle of the quantised variants) */
 void oracle_gemm_f32_rows(int N, int K, const float *X, const float *W, float *Y,
                           const int *rows, int n_rows, int strict)
 {
-#pragma omp parallel for schedule(dynamic, 1)
-    for (int i = 0; i < n_rows; i++) {
-        int r = rows ? rows[i] : i;
-        const float *x = X + (size_t)r * K;
-        float *y = Y + (size_t)i * N;
-        if (strict) {
-            for (int c = 0; c < N; c++)
-                y[c] = dot_strict(x, W + (size_t)c * K, K);
-            continue;
-        }
-        int c = 0;
-        for (; c + 4 <= N; c += 4) {
-            const float *w0 = W + (size_t)c * K, *w1 = w0 + K, *w2 = w1 + K, *w3 = w2 + K;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma omp simd reduction(+ : a0, a1, a2, a3)
-            for (int k = 0; k < K; k++) {
-                float xv = x[k];
-                a0 += xv * w0[k];
-                a1 += xv * w1[k];
-                a2 += xv * w2[k];
-                a3 += xv * w3[k];
-            }
-            y[c] = a0; y[c + 1] = a1; y[c + 2] = a2; y[c + 3] = a3;
-        }
-        for (; c < N; c++) {
-            const float *w0 = W + (size_t)c * K;
-            float a0 = 0.f;
-#pragma omp simd reduction(+ : a0)
-            for (int k = 0; k < K; k++)
-                a0 += x[k] * w0[k];
-            y[c] = a0;
-        }
-    }
+    gemm_rows_f32(N, K, X, W, Y, rows, n_rows, strict);
 }
 
 /*
  * bf16 in, FP32 out.  The reference's oracle signature (src/bench.cu:87-95:
  * naive_gemm_f32(M,N,K,X,W,Y)) with two additions: a row list and the strict flag.
- * Returns 0, or -1 when scratch memory cannot be had.
  */
 int oracle_gemm_bf16_rows(int M, int N, int K, const uint16_t *X, const uint16_t *W,
                           float *Y, const int *rows, int n_rows, int strict)
 {
     (void)M;
-    float *Wf = (float *)malloc((size_t)N * K * sizeof(float));
-    float *Xf = (float *)malloc((size_t)n_rows * K * sizeof(float));
-    if (!Wf || !Xf) { free(Wf); free(Xf); return -1; }
-    oracle_bf16_to_f32(W, Wf, (size_t)N * K);
-    for (int i = 0; i < n_rows; i++) {
-        int r = rows ? rows[i] : i;
-        for (int k = 0; k < K; k++)
-            Xf[(size_t)i * K + k] = bf16_to_f32(X[(size_t)r * K + k]);
-    }
-    oracle_gemm_f32_rows(N, K, Xf, Wf, Y, NULL, n_rows, strict);
-    free(Wf); free(Xf);
+    gemm_rows_bf16(N, K, X, W, Y, rows, n_rows, strict);
     return 0;
 }
 

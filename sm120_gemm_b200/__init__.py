@@ -215,5 +215,25 @@ def dispatch_ex(kernel: LoadedKernel, args: GemmArgs) -> None:
         raise GemmError(rc, kernel.last_error()[1])
 
 
-__all__ = ["GemmConfig", "generate_configs", "KernelRegistry", "AutotuneCache", "LoadedKernel", "GemmArgs", "GemmError",
+_UTIL = None
+
+
+def util_lib() -> ctypes.CDLL:
+    """``libsm100gemm_util.so``: gemm_interleave_blocks, gemm_spacer (csrc/gemm_util.cu)."""
+    global _UTIL
+    if _UTIL is None:
+        path = os.path.join(KERNEL_DIR, "libsm100gemm_util.so")
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{path} is missing: run __graft_entry__.build() or python -m sm120_gemm_b200.build")
+        lib = ctypes.CDLL(path)
+        lib.gemm_interleave_blocks.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_int,
+                                               ctypes.c_int, ctypes.c_void_p]
+        lib.gemm_interleave_blocks.restype = ctypes.c_int
+        lib.gemm_spacer.argtypes = [ctypes.c_uint, ctypes.c_void_p]
+        lib.gemm_spacer.restype = ctypes.c_int
+        _UTIL = lib
+    return _UTIL
+
+
+__all__ = ["util_lib", "GemmConfig", "generate_configs", "KernelRegistry", "AutotuneCache", "LoadedKernel", "GemmArgs", "GemmError",
            "dispatch", "dispatch_ex", "load_plugin", "KERNEL_DIR", "ABI_SYMBOLS"]

@@ -59,9 +59,25 @@ def build_one(cfg: GemmConfig, force: bool = False, verbose: bool = False) -> st
     return out
 
 
+UTIL_LIB = os.path.join(KERNEL_DIR, "libsm100gemm_util.so")
+
+
+def build_util(force: bool = False) -> str:
+    """The utility library (block interleave for the N-sharded run, timing spacer)."""
+    src = os.path.join(CSRC, "gemm_util.cu")
+    if not force and os.path.exists(UTIL_LIB) and os.path.getmtime(UTIL_LIB) >= os.path.getmtime(src):
+        return UTIL_LIB
+    os.makedirs(KERNEL_DIR, exist_ok=True)
+    r = subprocess.run([NVCC, *NVCC_FLAGS, "-o", UTIL_LIB, src], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for gemm_util.cu:\n{r.stdout}\n{r.stderr}")
+    return UTIL_LIB
+
+
 def build_all(configs=None, force: bool = False, jobs: int | None = None) -> list[str]:
     configs = list(configs) if configs is not None else generate_configs()
     jobs = jobs or max(1, (os.cpu_count() or 2))
+    build_util(force)
     with ThreadPoolExecutor(jobs) as ex:
         return list(ex.map(lambda c: build_one(c, force), configs))
 

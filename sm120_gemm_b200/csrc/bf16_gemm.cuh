@@ -29,6 +29,7 @@
 
 #include "gemm_host.h"
 #include "ptx_sm100.cuh"
+#include "tile_order.h"
 #include "umma_desc.h"
 
 using bf16 = __nv_bfloat16;
@@ -48,20 +49,6 @@ struct GemmParams {
     float alpha;          // epilogue scale (FP8 per-tensor: sx*sw)
     uint32_t *status;
 };
-
-// Tile order: bands of `group_n` tile columns, walked row by row inside a band, so the CTAs
-// running at one time cover a compact block of Y and share X and W tiles through L2.
-// (Same purpose as the reference's rasterize_tile, src/bf16_gemm.cuh:225-237.)
-__host__ __device__ __forceinline__ void tile_to_mn(int tile, int num_m, int num_n, int group_n, int &mb, int &nb)
-{
-    int per_band = group_n * num_m;
-    int band = tile / per_band;
-    int rem = tile - band * per_band;
-    int n_first = band * group_n;
-    int width = num_n - n_first < group_n ? num_n - n_first : group_n;
-    mb = rem / width;
-    nb = n_first + (rem - mb * width);
-}
 
 template <int OPK_, int BN_, int STAGES_, int CG_, int SPLIT_K_, int EPI_>
 struct UmmaGemmTraits {

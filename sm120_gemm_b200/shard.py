@@ -1,0 +1,88 @@
+"""N-sharding of Y = X * W^T across the GPUs of one node (one process per GPU).
+
+Rank r holds the contiguous weight rows W[r*N/g : (r+1)*N/g, :] and the full X, computes its
+M x N/g column block of Y with a kernel plugin, and one NCCL all-gather over NVLink collects
+the blocks; a device interleave kernel turns the gathered [g][M][N/g] buffer into the
+row-major M x N result every rank ends up with.  K is never split across GPUs, so there is no
+reduction.  The reference is single-GPU (device 0 hard-coded, src/bf16_gemm.cuh:531); this
+module has no counterpart there.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class ShardPlan:
+    world: int
+    rank: int
+    N: int
+    row_start: int   # first weight row (= first Y column) of this rank
+    rows: int        # weight rows (= Y columns) of this rank
+
+
+def shard_plan(N: int, world: int, rank: int) -> ShardPlan:
+    """Equal contiguous row blocks.  A shape shards only when every block keeps a 16-byte
+    row pitch (N/g a multiple of 8 bf16 elements)."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} of {world}")
+    if N % world != 0 or (N // world) % 8 != 0:
+        raise ValueError(f"N={N} does not shard across {world} GPUs in multiples of 8 columns")
+    nb = N // world
+    return ShardPlan(world, rank, N, rank * nb, nb)
+
+
+def blocked_to_row_major_index(plan_world: int, M: int, nb: int, m: int, n: int) -> int:
+    """Flat index into the gathered [g][M][nb] buffer of the element that belongs at Y[m, n]
+    (the mapping the interleave kernel implements)."""
+    r, j = divmod(n, nb)
+    assert r < plan_world
+    return (r * M + m) * nb + j
+
+
+class NShardedGemm:
+    """Per-rank GEMM + all-gather + interleave on the current CUDA device.
+
+    ``kernel`` is a LoadedKernel; tensors are torch CUDA tensors (bf16).  The all-gather is
+    issued on ``comm_stream`` when given so that it can overlap the next compute step.
+    """
+
+    def __init__(self, kernel, M: int, N: int, K: int, rank: int, world: int, group=None):
+        import torch
+
+        from . import util_lib
+
+        self.torch = torch
+        self.kernel = kernel
+        self.M, self.N, self.K = M, N, K
+        self.plan = shard_plan(N, world, rank)
+        self.group = group
+        self.util = util_lib()
+        if not kernel.can_run(M, self.plan.rows, K):
+            raise ValueError(f"{kernel.config.name()} cannot run the {M}x{self.plan.rows}x{K} shard")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.y_local = torch.empty((M, self.plan.rows), dtype=torch.bfloat16, device=dev)
+        self.blocked = torch.empty((world, M, self.plan.rows), dtype=torch.bfloat16, device=dev) if world > 1 else None
+        wsb = kernel.workspace_bytes(M, self.plan.rows, K)
+        self.ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+        self.ws_ptr = self.ws.data_ptr() if wsb else 0
+
+    def run(self, X, W_shard, Y_out):
+        """Y_out (M x N, row-major) <- X @ W^T, where this rank passes only its rows of W."""
+        import torch.distributed as dist
+
+        from . import dispatch
+
+        t = self.torch
+        stream = t.cuda.current_stream().cuda_stream
+        if self.plan.world == 1:
+            dispatch(self.kernel, self.M, self.N, self.K, X.data_ptr(), W_shard.data_ptr(), Y_out.data_ptr(), self.ws_ptr, stream)
+            return 1
+        dispatch(self.kernel, self.M, self.plan.rows, self.K, X.data_ptr(), W_shard.data_ptr(), self.y_local.data_ptr(),
+                 self.ws_ptr, stream)
+        dist.all_gather_into_tensor(self.blocked, self.y_local, group=self.group)
+        rc = self.util.gemm_interleave_blocks(self.blocked.data_ptr(), Y_out.data_ptr(), self.plan.world, self.M, self.plan.rows, 2,
+                                              stream)
+        if rc != 0:
+            raise RuntimeError(f"gemm_interleave_blocks failed with CUDA error {rc}")
+        return 2  # kernels of this library launched (GEMM + interleave); split-K adds its reduce

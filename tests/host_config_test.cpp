@@ -1,0 +1,95 @@
+// Host-only checks of csrc/gemm_config.h and csrc/tile_order.h (compiled with g++ and run by
+// tests/test_host_config.py).  Prints "OK <n>" on success; any failed check prints and exits 1.
+#include <cstdio>
+#include <cstdlib>
+#include <fstream>
+#include <set>
+
+#include "../sm120_gemm_b200/csrc/gemm_config.h"
+#include "../sm120_gemm_b200/csrc/tile_order.h"
+#include "../sm120_gemm_b200/csrc/umma_desc.h"
+
+static int checks = 0;
+#define CHECK(cond)                                                          \
+    do {                                                                     \
+        checks++;                                                            \
+        if (!(cond)) {                                                       \
+            std::printf("FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond);    \
+            std::exit(1);                                                    \
+        }                                                                    \
+    } while (0)
+
+int main(int argc, char **argv)
+{
+    // name <-> struct round trip, strictness of the parser
+    GemmConfig c;
+    c.dt = GEMM_DT_FP8; c.bm = 256; c.bn = 192; c.bk = 128; c.num_stages = 6; c.cg = 2; c.split_k = 4; c.swap_ab = 0; c.epi = 0;
+    CHECK(c.name() == "fp8_bm256_bn192_bk128_s6_cg2_sk4_ab0_e0");
+    auto p = GemmConfig::parse(c.name());
+    CHECK(p && p->name() == c.name() && p->dt == GEMM_DT_FP8 && p->split_k == 4);
+    CHECK(!GemmConfig::parse("bm128_bn64_bk64_s3_cwg2_wm32_wn32_sk1"));   // the reference's old names are not plugins of this build
+    CHECK(!GemmConfig::parse("bf16_bm128_bn128_bk64_s4_cg1_sk1_ab0_e1_extra"));
+    CHECK(!GemmConfig::parse("int8_bm128_bn128_bk64_s4_cg1_sk1_ab0_e1"));
+
+    // validity: ragged M/N/K are fine, pitches must be 16-byte multiples, split-K needs whole equal slices
+    GemmConfig b = *GemmConfig::parse("bf16_bm128_bn128_bk64_s4_cg1_sk1_ab0_e1");
+    CHECK(b.is_valid_for(1, 8, 8) && b.is_valid_for(100, 136, 200));
+    CHECK(!b.is_valid_for(128, 130, 64) && !b.is_valid_for(128, 128, 60) && !b.is_valid_for(0, 128, 64));
+    GemmConfig sk = *GemmConfig::parse("bf16_bm128_bn128_bk64_s7_cg1_sk4_ab0_e0");
+    CHECK(sk.is_valid_for(128, 4096, 14336) && !sk.is_valid_for(128, 4096, 14336 + 64) && !sk.is_valid_for(128, 128, 200));
+
+    // cache: round trip, legacy three-field keys, malformed lines skipped, atomic replace
+    const std::string path = argc > 1 ? argv[1] : "/tmp/sm100_cache_test.txt";
+    {
+        std::ofstream f(path);
+        f << "# comment\n"
+          << "1024,1024,1024 bf16_bm128_bn128_bk64_s4_cg1_sk1_ab0_e1 0.0123\n"        // reference-format key
+          << "fp8,1,8192,8192,8192 fp8_bm256_bn256_bk128_s6_cg2_sk1_ab0_e1 0.3\n"
+          << "bf16,8,16384,16384,16384 bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1 1.5\n"
+          << "garbage line\n"
+          << "1,2 bf16_bm128_bn128_bk64_s4_cg1_sk1_ab0_e1 1.0\n"
+          << "4096,4096,4096 not_a_config 1.0\n";
+    }
+    AutotuneCache cache;
+    cache.quiet = true;
+    CHECK(cache.load(path) && cache.entries.size() == 3);
+    CHECK(cache.lookup(1024, 1024, 1024) && cache.lookup(1024, 1024, 1024)->time_ms == 0.0123);
+    CHECK(cache.lookup(8192, 8192, 8192, GEMM_DT_FP8) && !cache.lookup(8192, 8192, 8192));
+    CHECK(cache.lookup(16384, 16384, 16384, GEMM_DT_BF16, 8) && !cache.lookup(16384, 16384, 16384, GEMM_DT_BF16, 1));
+    cache.store(128, 4096, 14336, sk, 0.02);
+    CHECK(cache.save(path));
+    AutotuneCache again;
+    again.quiet = true;
+    CHECK(again.load(path) && again.entries.size() == 4 && again.lookup(128, 4096, 14336)->config.name() == sk.name());
+    AutotuneCache missing;
+    CHECK(!missing.load(path + ".does_not_exist"));
+
+    // registry: missing directory is reported, not fatal
+    KernelRegistry none;
+    none.quiet = true;
+    CHECK(!none.load_dir("/nonexistent/kernel/dir"));
+
+    // tile order is a bijection onto the grid for awkward sizes, including a narrower last band
+    for (int num_m : {1, 3, 32, 64})
+        for (int num_n : {1, 5, 16, 37})
+            for (int group : {1, 4, 8, 16}) {
+                std::set<std::pair<int, int>> seen;
+                for (int t = 0; t < num_m * num_n; t++) {
+                    int mb, nb;
+                    sm100::tile_to_mn(t, num_m, num_n, group, mb, nb);
+                    CHECK(mb >= 0 && mb < num_m && nb >= 0 && nb < num_n);
+                    seen.insert({mb, nb});
+                }
+                CHECK((int)seen.size() == num_m * num_n);
+            }
+
+    // descriptor builders: field positions
+    const uint64_t d = sm100::make_smem_desc_k128(0x12400);
+    CHECK((d & 0x3fff) == (0x12400 >> 4) && ((d >> 32) & 0x3fff) == 64 && ((d >> 46) & 3) == 1 && (d >> 61) == 2);
+    CHECK(sm100::advance_desc_k(d, 3) - d == 6);
+    const uint32_t i = sm100::make_idesc(sm100::UMMA_BF16, sm100::UMMA_BF16, 256, 192);
+    CHECK(((i >> 4) & 3) == 1 && ((i >> 7) & 7) == 1 && ((i >> 10) & 7) == 1 && ((i >> 17) & 63) == 24 && ((i >> 24) & 31) == 16);
+
+    std::printf("OK %d\n", checks);
+    return 0;
+}

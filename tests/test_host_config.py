@@ -1,0 +1,100 @@
+"""CPU tests of the host side: configuration names, validity rules, the shared-memory model,
+the autotune cache, plugin loading (every ABI symbol) and error reporting -- in the Python
+mirror and, through a compiled test program, in the C++ header a C++ caller includes."""
+import ctypes
+import os
+import re
+import subprocess
+
+import pytest
+
+import sm120_gemm_b200 as g
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_cpp_header_checks(tmp_path):
+    exe = tmp_path / "host_config_test"
+    subprocess.check_call(["/usr/bin/g++", "-std=c++17", "-O1", "-I/usr/local/cuda/include", "-o", str(exe),
+                           os.path.join(ROOT, "tests", "host_config_test.cpp"), "-ldl"])
+    out = subprocess.run([str(exe), str(tmp_path / "cache.txt")], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.strip().startswith("OK"), out.stdout + out.stderr
+
+
+def test_config_name_roundtrip_all_generated():
+    cfgs = g.generate_configs()
+    assert len(cfgs) == len({c.name() for c in cfgs}) > 40
+    for c in cfgs:
+        assert g.GemmConfig.parse(c.name()) == c
+        assert c.bm == 128 * c.cg and c.smem_bytes() <= 232448
+    assert g.GemmConfig.parse("bm128_bn64_bk64_s3_cwg2_wm32_wn32_sk1") is None
+    assert g.GemmConfig.parse("bf16_bm128_bn128_bk64_s4_cg1_sk1_ab0_e1x") is None
+
+
+def test_registry_loads_every_plugin_and_symbol(registry):
+    names = {k.config.name() for k in registry.kernels}
+    built = {f[len("libgemm_"):-3] for f in os.listdir(g.KERNEL_DIR) if f.startswith("libgemm_") and f.endswith(".so")}
+    assert names == built
+    header = open(os.path.join(ROOT, "include", "sm100_gemm.h")).read()
+    declared = set(re.findall(r"\b(gemm_[a-z_]+)\s*\(", header))
+    assert declared == set(g.ABI_SYMBOLS)
+    for k in registry.kernels:
+        for sym in declared:
+            assert getattr(k.lib, sym) is not None
+        assert k.lib.gemm_config_name().decode() == k.config.name()
+        # the host-side shared-memory model must equal what the kernel was compiled with
+        assert k.smem_bytes() == k.config.smem_bytes()
+
+
+def test_validity_rules_match_plugins(registry):
+    shapes = [(1, 8, 8), (128, 128, 64), (100, 136, 200), (128, 130, 64), (128, 128, 60), (128, 4096, 14336),
+              (128, 4096, 14400), (16, 28672, 8192), (0, 8, 8), (1024, 1024, 1000)]
+    for k in registry.kernels:
+        for (M, N, K) in shapes:
+            assert bool(k.can_run(M, N, K)) == k.config.is_valid_for(M, N, K), (k.config.name(), M, N, K)
+        if k.config.split_k > 1:
+            assert k.workspace_bytes(128, 4096, 14336) == k.config.split_k * 128 * 4096 * 4
+        else:
+            assert k.workspace_bytes(128, 4096, 14336) == 0
+
+
+def test_errors_are_reported_not_fatal(registry):
+    """No launch can happen here (no GPU); argument and shape errors must come back as codes."""
+    k = next(k for k in registry.kernels if k.config.dt == "bf16" and k.config.split_k == 1)
+    k.lib.gemm_run(128, 130, 64, 0, 0, 0, 0, 0)          # N not a multiple of 8
+    code, msg = k.last_error()
+    assert code == 1 and "not supported" in msg
+    k.lib.gemm_run(128, 128, 64, 0, 0, 0, 0, 0)          # null pointers
+    assert k.last_error()[0] == 6
+    args = g.GemmArgs()
+    args.struct_size = 4
+    assert k.lib.gemm_run_ex(ctypes.byref(args)) == 6    # wrong struct size
+    args.struct_size = ctypes.sizeof(g.GemmArgs)
+    args.dtype = 3
+    assert k.lib.gemm_run_ex(ctypes.byref(args)) == 6    # dtype does not match the plugin
+    sk = next(k for k in registry.kernels if k.config.dt == "bf16" and k.config.split_k == 4)
+    with pytest.raises(g.GemmError) as e:
+        g.dispatch(sk, 128, 128, 256, 16, 16, 16, 0, 0)  # split-K without a workspace
+    assert e.value.code == 4
+    fp8 = next((k for k in registry.kernels if k.config.dt == "fp8"), None)
+    if fp8 is not None:
+        fp8.lib.gemm_run(128, 128, 128, 16, 16, 16, 0, 0)
+        assert fp8.last_error()[0] == 6                  # gemm_run is the bf16 entry point
+
+
+def test_autotune_cache_roundtrip(tmp_path):
+    p = tmp_path / "cache.txt"
+    p.write_text("# c\n1024,1024,1024 bf16_bm128_bn128_bk64_s4_cg1_sk1_ab0_e1 0.0123\n"
+                 "bf16,8,16384,16384,16384 bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1 1.5\nbad line\n"
+                 "1,2,3 nonsense 1.0\n")
+    c = g.AutotuneCache()
+    assert c.load(str(p)) and len(c.entries) == 2
+    assert c.lookup(1024, 1024, 1024)[1] == 0.0123
+    assert c.lookup(16384, 16384, 16384, gpus=8) and not c.lookup(16384, 16384, 16384)
+    cfg = g.GemmConfig.parse("bf16_bm128_bn64_bk64_s8_cg1_sk2_ab0_e0")
+    c.store(128, 4096, 14336, cfg, 0.02)
+    c.save(str(p))
+    d = g.AutotuneCache()
+    d.load(str(p))
+    assert d.entries == c.entries
+    assert not g.AutotuneCache().load(str(tmp_path / "missing.txt"))
