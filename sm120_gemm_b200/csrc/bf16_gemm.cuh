@@ -27,6 +27,8 @@
 #pragma once
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "gemm_host.h"
 #include "ptx_sm100.cuh"
 #include "tile_order.h"
@@ -350,6 +352,18 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
 }
 
 // ---------------------------------------------------------------------------------- host side
+// Width of a rasterisation band in tiles.  SM100_GEMM_GROUP_N overrides the built-in choice
+// (read once; meant for tuning runs).
+inline int band_width(int bn)
+{
+    static const int override_n = []() {
+        const char *e = std::getenv("SM100_GEMM_GROUP_N");
+        return e ? std::atoi(e) : 0;
+    }();
+    if (override_n > 0) return override_n;
+    return bn >= 256 ? 8 : 16;
+}
+
 template <class T>
 struct UmmaGemmLauncher {
     static bool can_run(int M, int N, int K)
@@ -450,7 +464,7 @@ struct UmmaGemmLauncher {
         p.num_m_blocks = (M + T::BM - 1) / T::BM;
         p.num_n_blocks = (N + T::BN - 1) / T::BN;
         p.num_k_blocks = ((K + T::BK - 1) / T::BK) / T::SPLIT_K;
-        p.group_n = (T::BN >= 256) ? 8 : 16;
+        p.group_n = band_width(T::BN);
         p.Y = Y;
         p.workspace = workspace;
         p.alpha = alpha;
