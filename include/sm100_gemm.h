@@ -100,6 +100,29 @@ int gemm_can_run(int M, int N, int K);
  * GemmConfig::smem_bytes, src/gemm_config.h:40-45). */
 size_t gemm_smem_bytes(void);
 
+/*
+ * BF16 split-K GEMM for callers that must not allocate device memory.  No counterpart in the
+ * reference (there the caller always brings the split-K workspace, src/bf16_gemm.cuh:601).
+ *
+ * Who needs it: code that runs where a device allocation is off the table -- a serving loop
+ * that may not take the device-wide synchronisation cudaMalloc/cudaFree imply, a host that has
+ * handed the whole GPU to its own memory pool and gives libraries no allocator, or a component
+ * that is simply not allowed to own device memory.  Such a caller still passes X, W and Y; the
+ * FP32 partial sums go into a fixed 16 MiB array compiled into the plugin
+ * (GEMM_NO_ALLOC_SCRATCH_BYTES), so the shape must satisfy SPLIT_K*M*N*4 <= 16 MiB, else the
+ * call fails with GEMM_ERR_WORKSPACE and launches nothing.  Plugins without split-K have no
+ * scratch and answer GEMM_ERR_ARG.  The call itself performs no cudaMalloc / cudaFree.
+ *
+ * The first call on each device looks up the array's device address (and does the library's
+ * usual one-time kernel-attribute set-up); make that first call outside any stream capture.
+ * All calls on a device share the one array: two calls whose kernels can overlap on the GPU
+ * (different streams, no dependency) race on it -- keep them on one stream or order them.
+ * Nothing in the array needs clearing between calls: each call overwrites every partial sum
+ * it later reads.  Every GPU that loads the plugin keeps the 16 MiB until the process ends.
+ */
+#define GEMM_NO_ALLOC_SCRATCH_BYTES ((size_t)16 << 20)
+int gemm_run_no_alloc(int M, int N, int K, const void *X, const void *W, void *Y, gemm_stream_t stream);
+
 /* Error of the last gemm_run / gemm_run_ex on this thread, and its text. */
 int gemm_last_error(void);
 const char *gemm_last_error_message(void);

@@ -24,7 +24,8 @@ ERROR_NAMES = {0: "GEMM_OK", 1: "GEMM_ERR_SHAPE", 2: "GEMM_ERR_CUDA", 3: "GEMM_E
 
 # every symbol include/sm100_gemm.h declares
 ABI_SYMBOLS = ("gemm_run", "gemm_run_ex", "gemm_config_name", "gemm_workspace_bytes", "gemm_can_run", "gemm_smem_bytes",
-               "gemm_last_error", "gemm_last_error_message", "gemm_check_status")
+               "gemm_last_error", "gemm_last_error_message", "gemm_check_status", "gemm_run_no_alloc")
+NO_ALLOC_SCRATCH_BYTES = 16 << 20  # GEMM_NO_ALLOC_SCRATCH_BYTES of include/sm100_gemm.h
 
 
 class GemmError(RuntimeError):
@@ -89,6 +90,8 @@ def _bind(lib: ctypes.CDLL) -> None:
     lib.gemm_last_error.restype = i32
     lib.gemm_last_error_message.restype = ctypes.c_char_p
     lib.gemm_check_status.restype = i32
+    lib.gemm_run_no_alloc.argtypes = [i32, i32, i32, vp, vp, vp, vp]
+    lib.gemm_run_no_alloc.restype = i32
 
 
 def load_plugin(path: str) -> LoadedKernel:

@@ -32,6 +32,17 @@ using Launcher = sm100::UmmaGemmLauncher<Traits>;
 #define GEMM_STR(x) GEMM_STR2(x)
 const char *const kConfigName = GEMM_STR(GEMM_NAME);
 
+// Scratch for gemm_run_no_alloc: lives in the plugin's own device image, so using it needs no
+// allocation call at all.  16 MiB = room for SPLIT_K*M*N <= 4 Mi FP32 partial sums (for example
+// 128 x 4096 outputs split 8 ways).  Every GPU that loads this plugin holds the array until the
+// process exits.  Only split-K configurations have scratch to place here.
+#if GEMM_SK > 1
+constexpr size_t kStaticScratchBytes = GEMM_NO_ALLOC_SCRATCH_BYTES;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+#else
+constexpr size_t kStaticScratchBytes = 0;
+#endif
+
 }  // namespace
 
 extern "C" {
@@ -62,6 +73,44 @@ int gemm_can_run(int M, int N, int K) { return Launcher::can_run(M, N, K) ? 1 : 
 size_t gemm_smem_bytes(void) { return Traits::SMEM_ALLOC; }
 int gemm_last_error(void) { return sm100::error_state().code; }
 const char *gemm_last_error_message(void) { return sm100::error_state().msg; }
+
+int gemm_run_no_alloc(int M, int N, int K, const void *X, const void *W, void *Y, gemm_stream_t stream)
+{
+    sm100::clear_error();
+#if GEMM_SK > 1
+    if (DT != GEMM_DT_BF16) return sm100::set_error(GEMM_ERR_ARG, "gemm_run_no_alloc takes bf16 operands; %s does not", kConfigName);
+    if (!Launcher::can_run(M, N, K)) return sm100::set_error(GEMM_ERR_SHAPE, "shape %dx%dx%d not supported by %s", M, N, K, kConfigName);
+    const size_t need = Launcher::workspace_bytes(M, N, K);
+    if (need > kStaticScratchBytes)
+        return sm100::set_error(GEMM_ERR_WORKSPACE,
+                                "gemm_run_no_alloc: %s needs %zu bytes of split-K scratch for %dx%dx%d but the built-in array has %zu; "
+                                "use gemm_run with a caller-owned workspace",
+                                kConfigName, need, M, N, K, kStaticScratchBytes);
+    // In host code `g_static_scratch` is only a handle for the symbol, not an address the GPU can
+    // use: the device address is looked up once per device, with that device current.
+    static float *scratch_on_device[sm100::MAX_DEVICES] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    SM100_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= sm100::MAX_DEVICES) return sm100::set_error(GEMM_ERR_ARG, "device ordinal %d out of range", dev);
+    float *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (scratch_on_device[dev] == nullptr) {
+            void *p = nullptr;
+            SM100_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+            scratch_on_device[dev] = static_cast<float *>(p);
+        }
+        scratch = scratch_on_device[dev];
+    }
+    // every partial sum the reduce kernel reads is written by this call's GEMM kernel first, so
+    // nothing in the array has to start at zero and the previous call's contents do not matter
+    return Launcher::run(M, N, K, X, W, Y, scratch, kStaticScratchBytes, 1.0f, 0, stream);
+#else
+    (void)M; (void)N; (void)K; (void)X; (void)W; (void)Y; (void)stream;
+    return sm100::set_error(GEMM_ERR_ARG, "gemm_run_no_alloc: %s uses no scratch memory; call gemm_run", kConfigName);
+#endif
+}
 
 int gemm_check_status(void)
 {
