@@ -44,13 +44,79 @@ enum : int { EPI_DIRECT = 0, EPI_TMA = 1 };     // epilogue: register->global st
 struct GemmParams {
     int M, N, K;
     int num_m_blocks, num_n_blocks;
-    int num_k_blocks;     // per split
+    int num_k_blocks;     // per split (stream-K: per tile)
     int group_n;          // width (in N tiles) of a rasterisation band
+    int burst;            // k-blocks the producer requests together (1 .. STAGES)
     void *Y;              // bf16 output (direct epilogue)
     float *workspace;     // split-K partial sums [split][M][N]
     float alpha;          // epilogue scale (FP8 per-tensor: sx*sw)
     uint32_t *status;
 };
+
+// One piece of work for a CTA (or CTA pair): accumulate `kb_count` k-blocks of one output tile.
+struct WorkItem {
+    int tile;       // output tile, rasterised by tile_to_mn
+    int kb_begin;   // first k-block (units of BK elements)
+    int kb_count;
+    int part;       // -1: the whole K range -> bf16 output; >= 0: FP32 partial (split index, or stream-K slot 0/1)
+};
+
+// Work distribution.  SPLIT_K >= 1: tiles x SPLIT_K equal K slices, dealt round-robin over the
+// persistent grid (the reference's virtual-tile scheme, src/bf16_gemm.cuh:654-655).
+// SPLIT_K == 0 ("stream-K"): the tiles x k-blocks units are cut into one contiguous, equally
+// long range per CTA, so every SM streams the same number of bytes whatever the tile count; a
+// range that does not cover a tile's whole K leaves an FP32 partial in the CTA's slot 0 (its
+// first item) or slot 1 (its last item), which streamk_reduce_kernel adds up in K order.
+template <int SPLIT_K>
+struct WorkSched {
+    long long u, u_begin, u_end;   // stream-K: unit range;  fixed: virtual tile index, stride, total
+    int kb_per_tile;
+    __device__ WorkSched(int cluster_id, int num_clusters, const GemmParams &p)
+    {
+        kb_per_tile = p.num_k_blocks;
+        if constexpr (SPLIT_K == 0) {
+            const long long units = (long long)p.num_m_blocks * p.num_n_blocks * kb_per_tile;
+            u_begin = units * cluster_id / num_clusters;
+            u_end = units * (cluster_id + 1) / num_clusters;
+            u = u_begin;
+        } else {
+            u = cluster_id;
+            u_begin = num_clusters;
+            u_end = (long long)p.num_m_blocks * p.num_n_blocks * SPLIT_K;
+        }
+    }
+    __device__ bool next(WorkItem &w)
+    {
+        if (u >= u_end) return false;
+        if constexpr (SPLIT_K == 0) {
+            w.tile = (int)(u / kb_per_tile);
+            w.kb_begin = (int)(u - (long long)w.tile * kb_per_tile);
+            const long long left = u_end - u;
+            w.kb_count = kb_per_tile - w.kb_begin < left ? kb_per_tile - w.kb_begin : (int)left;
+            const bool whole = (w.kb_begin == 0 && w.kb_count == kb_per_tile);
+            w.part = whole ? -1 : (u == u_begin ? 0 : 1);
+            u += w.kb_count;
+        } else {
+            w.tile = (int)(u / SPLIT_K);
+            const int split = (int)(u - (long long)w.tile * SPLIT_K);
+            w.kb_begin = split * kb_per_tile;
+            w.kb_count = kb_per_tile;
+            w.part = SPLIT_K > 1 ? split : -1;
+            u += u_begin;
+        }
+        return true;
+    }
+};
+
+// stream-K bookkeeping shared by the GEMM kernel and the reduce kernel
+__host__ __device__ __forceinline__ long long streamk_range_begin(long long units, int c, int num_clusters)
+{
+    return units * c / num_clusters;
+}
+__host__ __device__ __forceinline__ int streamk_owner(long long units, long long u, int num_clusters)
+{
+    return (int)(((u + 1) * num_clusters - 1) / units);   // the c with range_begin(c) <= u < range_begin(c+1)
+}
 
 template <int OPK_, int BN_, int STAGES_, int CG_, int SPLIT_K_, int EPI_>
 struct UmmaGemmTraits {
@@ -59,7 +125,7 @@ struct UmmaGemmTraits {
     static constexpr int STAGES = STAGES_;
     static constexpr int CG = CG_;
     static constexpr int SPLIT_K = SPLIT_K_;
-    static constexpr int EPI = (SPLIT_K_ > 1) ? EPI_DIRECT : EPI_;
+    static constexpr int EPI = (SPLIT_K_ > 1) ? EPI_DIRECT : EPI_;   // stream-K (0) keeps the chosen epilogue for whole tiles
     static constexpr int ELEM_BYTES = (OPK_ == OPK_BF16) ? 2 : 1;
     static constexpr int BM_CTA = 128;                     // rows of X (and of the accumulator) per CTA
     static constexpr int BM = BM_CTA * CG_;                // rows of the tile
@@ -140,8 +206,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = p.num_m_blocks * p.num_n_blocks * T::SPLIT_K;
-
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -149,30 +213,44 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             uint32_t phase = 0;
             const uint32_t full_leader = (CG == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
             bool ok = true;
-            for (int v = cluster_id; v < total_tiles && ok; v += num_clusters) {
-                const int tile = v / T::SPLIT_K, split = v - tile * T::SPLIT_K;
+            WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
+            WorkItem w;
+            while (ok && sched.next(w)) {
                 int mb, nb;
-                tile_to_mn(tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
+                tile_to_mn(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
                 const int row_x = mb * T::BM + (int)cta_rank * T::BM_CTA;
                 const int row_w = nb * BN + (int)cta_rank * T::BN_CTA;
-                const int kb0 = split * p.num_k_blocks;
-                for (int kb = 0; kb < p.num_k_blocks; kb++) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, stage)) {
-                        ok = false;
-                        break;
+                const int kb0 = w.kb_begin;
+                const int num_kb = w.kb_count;
+                // Loads are issued in bursts of `burst` consecutive k-blocks once that many ring
+                // slots are free, so each weight row is fetched in runs of burst*128 contiguous
+                // bytes at (nearly) the same time -- kinder to DRAM pages than 128 bytes at a time.
+                for (int kb = 0; kb < num_kb && ok; kb += p.burst) {
+                    const int nb_burst = num_kb - kb < p.burst ? num_kb - kb : p.burst;
+                    int st = stage;
+                    uint32_t ph = phase;
+                    for (int d = 0; d < nb_burst; d++) {
+                        if (!mbar_wait(empty_bar(st), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, st)) {
+                            ok = false;
+                            break;
+                        }
+                        if (++st == STAGES) { st = 0; ph ^= 1u; }
                     }
-                    const int kx = (kb0 + kb) * T::BK;
-                    if constexpr (CG == 1) {
-                        mbar_arrive_expect_tx(full_bar(stage), T::STAGE_BYTES);
-                        tma_load_2d(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x);
-                        tma_load_2d(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w);
-                    } else {
-                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
-                        const uint32_t fb = full_leader + 8u * stage;
-                        tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x);
-                        tma_load_2d_pair(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w);
+                    if (!ok) break;
+                    for (int d = 0; d < nb_burst; d++) {
+                        const int kx = (kb0 + kb + d) * T::BK;
+                        if constexpr (CG == 1) {
+                            mbar_arrive_expect_tx(full_bar(stage), T::STAGE_BYTES);
+                            tma_load_2d(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w);
+                            tma_load_2d(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x);
+                        } else {
+                            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
+                            const uint32_t fb = full_leader + 8u * stage;
+                            tma_load_2d_pair(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w);
+                            tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x);
+                        }
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                     }
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -185,13 +263,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             uint32_t phase = 0;
             int titer = 0;
             bool ok = true;
-            for (int v = cluster_id; v < total_tiles && ok; v += num_clusters, titer++) {
+            WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
+            WorkItem w;
+            for (; ok && sched.next(w); titer++) {
                 const int acc = titer & 1;
                 const uint32_t acc_phase = (titer >> 1) & 1;
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, acc)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < p.num_k_blocks; kb++) {
+                for (int kb = 0; kb < w.kb_count; kb++) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage)) {
                         ok = false;
                         break;
@@ -222,10 +302,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const uint32_t tempty_leader = (CG == 2) ? mapa_shared(tempty_bar(0), 0) : tempty_bar(0);
         int titer = 0;
         int buf = 0;
-        for (int v = cluster_id; v < total_tiles; v += num_clusters, titer++) {
-            const int tile = v / T::SPLIT_K, split = v - tile * T::SPLIT_K;
+        WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
+        WorkItem w;
+        for (; sched.next(w); titer++) {
             int mb, nb;
-            tile_to_mn(tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
+            tile_to_mn(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
             const int m0 = mb * T::BM + (int)cta_rank * T::BM_CTA;
             const int n0 = nb * BN;
             const int acc = titer & 1;
@@ -238,6 +319,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
             const int grow = m0 + row_in_tile;
 
+            if (T::SPLIT_K == 0 && w.part >= 0) {
+                // stream-K partial: the CTA's private slot, tile-local [BM][BN] layout, no bounds
+                float *slot = p.workspace + ((size_t)(2 * cluster_id + w.part) * T::BM + cta_rank * T::BM_CTA + row_in_tile) * BN;
+#pragma unroll 1
+                for (int j = 0; j < BN / 32; j++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + (uint32_t)(j * 32), r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 8; c++)
+                        *reinterpret_cast<uint4 *>(slot + j * 32 + c * 4) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                }
+            } else {
 #pragma unroll 1
             for (int j = 0; j < BN / 64; j++) {
                 uint32_t stg = 0;
@@ -255,7 +349,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     const int col0 = n0 + j * 64 + h * 32;
                     if constexpr (T::SPLIT_K > 1) {
                         if (grow < p.M) {
-                            float *dst = p.workspace + ((size_t)split * p.M + grow) * p.N + col0;
+                            float *dst = p.workspace + ((size_t)w.part * p.M + grow) * p.N + col0;
 #pragma unroll
                             for (int c = 0; c < 8; c++)
                                 if (col0 + c * 4 < p.N)
@@ -295,6 +389,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     }
                     buf ^= 1;
                 }
+            }
             }
             // accumulator buffer drained: hand it back to the MMA issuer
             tc_fence_before_sync();
@@ -351,7 +446,67 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
     }
 }
 
+// Adds up the stream-K partials of every tile that more than one CTA worked on and writes the
+// bf16 result; contributions are added in ascending K order (ascending CTA index).  Each tile
+// is cut into `parts` row slices (one block each) so that all SMs take part; 8 outputs per
+// thread, 128-bit loads and stores.  Tiles that one CTA computed whole were already written
+// by the GEMM kernel and are skipped.
+template <int BM, int BN>
+__global__ void __launch_bounds__(256) streamk_reduce_kernel(const float *__restrict__ ws, bf16 *__restrict__ Y, int M, int N,
+                                                             int num_m, int num_n, int group_n, int kb_per_tile,
+                                                             int num_clusters, int parts, float alpha)
+{
+    const int tile = blockIdx.x / parts, part = blockIdx.x - tile * parts;
+    const long long units = (long long)num_m * num_n * kb_per_tile;
+    const long long t0 = (long long)tile * kb_per_tile;
+    const int c_lo = streamk_owner(units, t0, num_clusters);
+    const int c_hi = streamk_owner(units, t0 + kb_per_tile - 1, num_clusters);
+    if (c_lo == c_hi) return;
+    int mb, nb;
+    tile_to_mn(tile, num_m, num_n, group_n, mb, nb);
+    const int rows_per_part = BM / parts;
+    constexpr int VEC_PER_ROW = BN / 8;
+    for (int it = threadIdx.x; it < rows_per_part * VEC_PER_ROW; it += blockDim.x) {
+        const int r = part * rows_per_part + it / VEC_PER_ROW;
+        const int c8 = (it % VEC_PER_ROW) * 8;
+        const int grow = mb * BM + r, gcol = nb * BN + c8;
+        if (grow >= M || gcol >= N) continue;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        for (int c = c_lo; c <= c_hi; c++) {
+            const int slot = streamk_range_begin(units, c, num_clusters) >= t0 ? 0 : 1;
+            const float4 *src = reinterpret_cast<const float4 *>(ws + ((size_t)(2 * c + slot) * BM + r) * BN + c8);
+            const float4 x = __ldcg(src), y = __ldcg(src + 1);
+            if (c == c_lo) { a = x; b = y; }
+            else {
+                a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+                b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+            }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(a.x * alpha, a.y * alpha);
+        o.y = pack_bf16x2(a.z * alpha, a.w * alpha);
+        o.z = pack_bf16x2(b.x * alpha, b.y * alpha);
+        o.w = pack_bf16x2(b.z * alpha, b.w * alpha);
+        *reinterpret_cast<uint4 *>(Y + (size_t)grow * N + gcol) = o;
+    }
+}
+
 // ---------------------------------------------------------------------------------- host side
+// Upper bound on resident CTAs used to size the stream-K workspace without asking a device.
+static constexpr int STREAMK_MAX_CTAS = 160;
+
+// k-blocks requested together by the TMA producer.  SM100_GEMM_BURST overrides (tuning runs).
+inline int load_burst(int stages)
+{
+    static const int override_b = []() {
+        const char *e = std::getenv("SM100_GEMM_BURST");
+        return e ? std::atoi(e) : 0;
+    }();
+    int b = override_b > 0 ? override_b : 1;
+    if (b > stages) b = stages;
+    return b;
+}
+
 // Width of a rasterisation band in tiles.  SM100_GEMM_GROUP_N overrides the built-in choice
 // (read once; meant for tuning runs).
 inline int band_width(int bn)
@@ -380,6 +535,8 @@ struct UmmaGemmLauncher {
     static size_t workspace_bytes(int M, int N, int K)
     {
         (void)K;
+        if (T::SPLIT_K == 0)   // two partial-tile slots per CTA (pair), whatever the shape
+            return (size_t)2 * (STREAMK_MAX_CTAS / T::CG) * T::BM * T::BN * sizeof(float);
         return T::SPLIT_K > 1 ? (size_t)T::SPLIT_K * M * N * sizeof(float) : 0;
     }
 
@@ -425,7 +582,7 @@ struct UmmaGemmLauncher {
     {
         if (!can_run(M, N, K)) return set_error(GEMM_ERR_SHAPE, "shape %dx%dx%d not supported by this configuration", M, N, K);
         if (!X || !W || !Y) return set_error(GEMM_ERR_ARG, "null operand pointer");
-        if (T::SPLIT_K > 1) {
+        if (T::SPLIT_K != 1) {
             if (!workspace) return set_error(GEMM_ERR_WORKSPACE, "split-K configuration needs a workspace");
             if (workspace_bytes_given != 0 && workspace_bytes_given < workspace_bytes(M, N, K))
                 return set_error(GEMM_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes_given, workspace_bytes(M, N, K));
@@ -463,16 +620,18 @@ struct UmmaGemmLauncher {
         p.M = M; p.N = N; p.K = K;
         p.num_m_blocks = (M + T::BM - 1) / T::BM;
         p.num_n_blocks = (N + T::BN - 1) / T::BN;
-        p.num_k_blocks = ((K + T::BK - 1) / T::BK) / T::SPLIT_K;
+        p.num_k_blocks = ((K + T::BK - 1) / T::BK) / (T::SPLIT_K > 0 ? T::SPLIT_K : 1);
         p.group_n = band_width(T::BN);
+        p.burst = load_burst(T::STAGES);
         p.Y = Y;
         p.workspace = workspace;
         p.alpha = alpha;
         p.status = dev->status;
-        const int total_tiles = p.num_m_blocks * p.num_n_blocks * T::SPLIT_K;
+        const long long work = (long long)p.num_m_blocks * p.num_n_blocks * (T::SPLIT_K > 0 ? T::SPLIT_K : p.num_k_blocks);
         int grid = 0;
-        rc = grid_size(*dev, total_tiles, sm_limit, &grid);
+        rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &grid);
         if (rc != GEMM_OK) return rc;
+        if (T::SPLIT_K == 0 && grid > STREAMK_MAX_CTAS) grid = STREAMK_MAX_CTAS - STREAMK_MAX_CTAS % T::CG;
 
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);
@@ -488,6 +647,15 @@ struct UmmaGemmLauncher {
         cfg.numAttrs = 1;
         SM100_CUDA_TRY(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T>, tx, tw, ty, p));
 
+        if (T::SPLIT_K == 0) {
+            const int tiles = p.num_m_blocks * p.num_n_blocks;
+            int parts = 1;
+            while (parts < 32 && tiles * parts < 2 * dev->sm_count) parts *= 2;
+            streamk_reduce_kernel<T::BM, T::BN><<<tiles * parts, 256, 0, stream>>>(workspace, static_cast<bf16 *>(Y), M, N, p.num_m_blocks,
+                                                                                  p.num_n_blocks, p.group_n, p.num_k_blocks,
+                                                                                  grid / T::CG, parts, alpha);
+            SM100_CUDA_TRY(cudaGetLastError());
+        }
         if (T::SPLIT_K > 1) {
             const size_t mn = (size_t)M * N;
             size_t blocks = (mn / 8 + 255) / 256;

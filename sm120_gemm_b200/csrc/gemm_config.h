@@ -42,7 +42,7 @@ struct GemmConfig {
     int dt = GEMM_DT_BF16;  // GEMM_DT_*
     int bm = 128, bn = 128, bk = 64, num_stages = 4;
     int cg = 1;             // CTA group: 1, or 2 for a CTA pair sharing one 256-row tile
-    int split_k = 1;
+    int split_k = 1;        // 1: none; >1: equal K slices + reduce; 0: stream-K (equal unit ranges per CTA)
     int swap_ab = 0;        // 1: W rows on the accumulator lanes (small-M shapes)
     int epi = 1;            // 0: register->global epilogue, 1: shared memory + TMA store
 
@@ -82,7 +82,7 @@ struct GemmConfig {
     size_t smem_bytes() const
     {
         const size_t a = 128 * 128, b = (size_t)(bn / cg) * 128;
-        const size_t staging = (split_k == 1 && epi == 1) ? 2 * 128 * 64 * 2 : 0;
+        const size_t staging = (split_k <= 1 && epi == 1) ? 2 * 128 * 64 * 2 : 0;
         const size_t barriers = (2 * (size_t)num_stages + 4) * 8 + 16;
         return num_stages * (a + b) + staging + barriers + 1024;
     }

@@ -108,7 +108,7 @@ int gemm_run_no_alloc(int M, int N, int K, const void *X, const void *W, void *Y
     return Launcher::run(M, N, K, X, W, Y, scratch, kStaticScratchBytes, 1.0f, 0, stream);
 #else
     (void)M; (void)N; (void)K; (void)X; (void)W; (void)Y; (void)stream;
-    return sm100::set_error(GEMM_ERR_ARG, "gemm_run_no_alloc: %s uses no scratch memory; call gemm_run", kConfigName);
+    return sm100::set_error(GEMM_ERR_ARG, "gemm_run_no_alloc: %s has no built-in scratch array; call gemm_run", kConfigName);
 #endif
 }
 

@@ -10,7 +10,8 @@ shared-memory cap for the mma.sync kernel), re-derived for the tcgen05 design:
   bk       one 128-byte swizzle span of K per stage: 64 bf16, 128 fp8, 256 fp4 elements
   s        TMA ring stages, bounded by the 227 KB of shared memory one CTA may use
   cg       CTA group (1 | 2)
-  sk       split-K factor (FP32 partials + reduce kernel)
+  sk       split-K factor (FP32 partials + reduce kernel); 0 = stream-K: the tiles x k-blocks work is
+           cut into one equal contiguous range per CTA, partial tiles are summed by a fix-up kernel
   ab       operand swap for small M (W rows on the 128 accumulator lanes)
   e        epilogue: 0 = registers -> global, 1 = swizzled shared memory -> TMA store
 
@@ -113,6 +114,10 @@ def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8")) -> list[Gemm
             for sk in (2, 4, 7, 8, 16):
                 s = min(max_stages(dt, bn, cg, sk, 0, max_smem), 8)
                 out.append(GemmConfig(dt, 128 * cg, bn, bk, s, cg, sk, 0, 0))
+        # stream-K: every SM streams the same number of bytes whatever the tile count
+        for cg, bn in ((1, 64), (1, 128), (1, 192), (1, 256), (2, 128), (2, 256)):
+            s = min(max_stages(dt, bn, cg, 0, 0, max_smem), 10)
+            out.append(GemmConfig(dt, 128 * cg, bn, bk, s, cg, 0, 0, 0))
     return out
 
 

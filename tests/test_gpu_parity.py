@@ -65,7 +65,8 @@ EDGE_SHAPES = [(1, 8, 8), (1, 64, 64), (16, 256, 512), (127, 264, 72), (129, 8, 
 
 
 @pytest.mark.parametrize("name", [BEST, "bf16_bm128_bn128_bk64_s6_cg1_sk1_ab0_e1", "bf16_bm128_bn128_bk64_s7_cg1_sk1_ab0_e0",
-                                  "bf16_bm256_bn192_bk64_s6_cg2_sk1_ab0_e1", "bf16_bm256_bn256_bk64_s7_cg2_sk1_ab0_e0"])
+                                  "bf16_bm256_bn192_bk64_s6_cg2_sk1_ab0_e1", "bf16_bm256_bn256_bk64_s7_cg2_sk1_ab0_e0",
+                                  "bf16_bm128_bn256_bk64_s4_cg1_sk0_ab0_e0", "bf16_bm256_bn256_bk64_s7_cg2_sk0_ab0_e0"])
 def test_ragged_and_tiny_shapes(registry, cuda_device, name):
     """M, N, K that are not multiples of the tile (the reference rejects these,
     src/gemm_config.h:34-38): partial tiles, a single k-block, exactly / one more than the ring depth."""
@@ -115,7 +116,7 @@ def test_config2_decode_shapes(registry, cuda_device, shape):
     Xd, Wd = to_dev(X), to_dev(W)
     ran = 0
     for k in bf16_plugins(registry):
-        if k.config.split_k not in (1, 4, 8) or not k.can_run(M, N, K) or k.config.epi == 0 and k.config.split_k == 1:
+        if k.config.split_k not in (0, 1, 4, 8) or not k.can_run(M, N, K) or k.config.epi == 0 and k.config.split_k == 1:
             continue
         dense_ok(to_bits(run_bf16(k, Xd, Wd)), ref, X, W, K)
         ran += 1
