@@ -141,10 +141,13 @@ struct UmmaGemmTraits {
     static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4;
     static constexpr int SMEM_BYTES = STAGES_ * STAGE_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + 16;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;   // slack to align the base to 1024 bytes
-    static constexpr int ACC_COLS = 2 * BN_;               // two FP32 accumulator buffers
+    static constexpr int ACC_STRIDE = (BN_ + 31) / 32 * 32;  // TMEM columns between the two accumulator buffers
+    static constexpr int ACC_COLS = 2 * ACC_STRIDE;        // two FP32 accumulator buffers
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
     static constexpr int THREADS = 256;
-    static_assert(BN_ % 64 == 0 && BN_ >= 64 && BN_ <= 256, "BN must be 64, 128, 192 or 256");
+    static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "BN (the UMMA N extent) is a multiple of 16 up to 256");
+    static_assert(EPI != EPI_TMA || BN_ % 64 == 0, "the TMA-store epilogue writes 64-column boxes");
+    static_assert((BN_ / CG_) % 8 == 0, "each CTA loads whole 8-row swizzle groups of W");
     static_assert(CG_ == 1 || CG_ == 2, "CTA group is 1 or 2");
     static_assert(STAGES_ >= 2, "at least two ring stages");
     static_assert(SMEM_ALLOC <= 232448, "exceeds the 227 KB of shared memory one CTA can have");
@@ -205,6 +208,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // split-K / stream-K: the reduce kernel that follows may be scheduled from now on (it blocks
+    // in griddepcontrol.wait until this grid has finished)
+    if constexpr (T::SPLIT_K != 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -270,7 +276,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 const uint32_t acc_phase = (titer >> 1) & 1;
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, acc)) break;
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * T::ACC_STRIDE);
                 for (int kb = 0; kb < w.kb_count; kb++) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage)) {
                         ok = false;
@@ -316,46 +322,60 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, acc);
             if (!named_bar_and(2, 128, got)) break;
             tc_fence_after_sync();
-            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * T::ACC_STRIDE);
             const int grow = m0 + row_in_tile;
+            // hands the drained accumulator buffer back to the MMA issuer
+            auto release_acc = [&]() {
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (CG == 1) mbar_arrive(tempty_bar(acc));
+                    else mbar_arrive_cluster(tempty_leader + 8u * acc);
+                }
+            };
 
             if (T::SPLIT_K == 0 && w.part >= 0) {
                 // stream-K partial: the CTA's private slot, tile-local [BM][BN] layout, no bounds
                 float *slot = p.workspace + ((size_t)(2 * cluster_id + w.part) * T::BM + cta_rank * T::BM_CTA + row_in_tile) * BN;
 #pragma unroll 1
-                for (int j = 0; j < BN / 32; j++) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(t_row + (uint32_t)(j * 32), r);
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x16(t_row + (uint32_t)c0, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 8; c++)
-                        *reinterpret_cast<uint4 *>(slot + j * 32 + c * 4) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                    for (int c = 0; c < 4; c++)
+                        *reinterpret_cast<uint4 *>(slot + c0 + c * 4) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
                 }
-            } else {
+                release_acc();
+            } else if constexpr (T::SPLIT_K > 1) {
+                // FP32 partial of this K slice into workspace[split][M][N]
 #pragma unroll 1
-            for (int j = 0; j < BN / 64; j++) {
-                uint32_t stg = 0;
-                if constexpr (T::EPI == EPI_TMA) {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x16(t_row + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    if (grow < p.M) {
+                        float *dst = p.workspace + ((size_t)w.part * p.M + grow) * p.N + n0 + c0;
+#pragma unroll
+                        for (int c = 0; c < 4; c++)
+                            if (n0 + c0 + c * 4 < p.N)
+                                *reinterpret_cast<uint4 *>(dst + c * 4) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                    }
+                }
+                release_acc();
+            } else if constexpr (T::EPI == EPI_TMA) {
+                // bf16 through swizzled shared memory and TMA stores of 128 x 64 boxes
+#pragma unroll 1
+                for (int j = 0; j < BN / 64; j++) {
                     // the store that last read this staging buffer must have finished reading it
                     if (epi_tid == 0) tma_store_wait_read<1>();
                     named_bar_sync(1, 128);
-                    stg = stg_base + buf * (T::BM_CTA * 128);
-                }
+                    const uint32_t stg = stg_base + buf * (T::BM_CTA * 128);
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(t_row + (uint32_t)(j * 64 + h * 32), r);
-                    tmem_ld_wait();
-                    const int col0 = n0 + j * 64 + h * 32;
-                    if constexpr (T::SPLIT_K > 1) {
-                        if (grow < p.M) {
-                            float *dst = p.workspace + ((size_t)w.part * p.M + grow) * p.N + col0;
-#pragma unroll
-                            for (int c = 0; c < 8; c++)
-                                if (col0 + c * 4 < p.N)
-                                    *reinterpret_cast<uint4 *>(dst + c * 4) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
-                        }
-                    } else {
+                    for (int h = 0; h < 2; h++) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(t_row + (uint32_t)(j * 64 + h * 32), r);
+                        tmem_ld_wait();
                         uint32_t pk[16];
 #pragma unroll
                         for (int i = 0; i < 16; i++) {
@@ -363,24 +383,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                             if constexpr (T::OPK != OPK_BF16) { lo *= p.alpha; hi *= p.alpha; }
                             pk[i] = pack_bf16x2(lo, hi);
                         }
-                        if constexpr (T::EPI == EPI_TMA) {
 #pragma unroll
-                            for (int c = 0; c < 4; c++) {
-                                const uint32_t chunk = (uint32_t)((h * 4 + c) ^ (row_in_tile & 7));
-                                st_shared_v4(stg + row_in_tile * 128 + chunk * 16, pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-                            }
-                        } else {
-                            if (grow < p.M) {
-                                bf16 *dst = static_cast<bf16 *>(p.Y) + (size_t)grow * p.N + col0;
-#pragma unroll
-                                for (int c = 0; c < 4; c++)
-                                    if (col0 + c * 8 < p.N)
-                                        *reinterpret_cast<uint4 *>(dst + c * 8) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-                            }
+                        for (int c = 0; c < 4; c++) {
+                            const uint32_t chunk = (uint32_t)((h * 4 + c) ^ (row_in_tile & 7));
+                            st_shared_v4(stg + row_in_tile * 128 + chunk * 16, pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
                         }
                     }
-                }
-                if constexpr (T::EPI == EPI_TMA) {
+                    if (j == BN / 64 - 1) release_acc();
                     fence_proxy_async_smem();
                     named_bar_sync(1, 128);
                     if (epi_tid == 0) {
@@ -389,14 +398,27 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     }
                     buf ^= 1;
                 }
-            }
-            }
-            // accumulator buffer drained: hand it back to the MMA issuer
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                if constexpr (CG == 1) mbar_arrive(tempty_bar(acc));
-                else mbar_arrive_cluster(tempty_leader + 8u * acc);
+            } else {
+                // bf16 straight from registers: 32 bytes per thread and step
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x16(t_row + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        float lo = __uint_as_float(r[2 * i]), hi = __uint_as_float(r[2 * i + 1]);
+                        if constexpr (T::OPK != OPK_BF16) { lo *= p.alpha; hi *= p.alpha; }
+                        pk[i] = pack_bf16x2(lo, hi);
+                    }
+                    if (grow < p.M) {
+                        bf16 *dst = static_cast<bf16 *>(p.Y) + (size_t)grow * p.N + n0 + c0;
+                        if (n0 + c0 < p.N) *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        if (n0 + c0 + 8 < p.N) *reinterpret_cast<uint4 *>(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                    }
+                }
+                release_acc();
             }
         }
         if constexpr (T::EPI == EPI_TMA) {
@@ -426,6 +448,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 template <int SPLIT_K>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ ws, bf16 *__restrict__ Y, size_t mn, float alpha)
 {
+    // launched as a programmatic dependent of the GEMM kernel: its blocks may already sit on the
+    // SMs while the GEMM drains; this waits (in hardware) until that grid is complete and visible
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t groups = mn / 8;
     for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += (size_t)gridDim.x * blockDim.x) {
         const float4 *src = reinterpret_cast<const float4 *>(ws + g * 8);
@@ -456,6 +481,7 @@ __global__ void __launch_bounds__(256) streamk_reduce_kernel(const float *__rest
                                                              int num_m, int num_n, int group_n, int kb_per_tile,
                                                              int num_clusters, int parts, float alpha)
 {
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // programmatic dependent of the GEMM kernel
     const int tile = blockIdx.x / parts, part = blockIdx.x - tile * parts;
     const long long units = (long long)num_m * num_n * kb_per_tile;
     const long long t0 = (long long)tile * kb_per_tile;
@@ -494,6 +520,26 @@ __global__ void __launch_bounds__(256) streamk_reduce_kernel(const float *__rest
 // ---------------------------------------------------------------------------------- host side
 // Upper bound on resident CTAs used to size the stream-K workspace without asking a device.
 static constexpr int STREAMK_MAX_CTAS = 160;
+
+// Launch configuration of a kernel that follows the GEMM kernel on the same stream as its
+// programmatic dependent (it calls griddepcontrol.wait before touching the GEMM's output).
+inline cudaLaunchConfig_t dependent_launch_config(unsigned blocks, unsigned threads, cudaStream_t stream)
+{
+    static cudaLaunchAttribute attr = []() {
+        cudaLaunchAttribute a;
+        a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        a.val.programmaticStreamSerializationAllowed = 1;
+        return a;
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cfg;
+}
 
 // k-blocks requested together by the TMA producer.  SM100_GEMM_BURST overrides (tuning runs).
 inline int load_burst(int stages)
@@ -651,18 +697,17 @@ struct UmmaGemmLauncher {
             const int tiles = p.num_m_blocks * p.num_n_blocks;
             int parts = 1;
             while (parts < 32 && tiles * parts < 2 * dev->sm_count) parts *= 2;
-            streamk_reduce_kernel<T::BM, T::BN><<<tiles * parts, 256, 0, stream>>>(workspace, static_cast<bf16 *>(Y), M, N, p.num_m_blocks,
-                                                                                  p.num_n_blocks, p.group_n, p.num_k_blocks,
-                                                                                  grid / T::CG, parts, alpha);
-            SM100_CUDA_TRY(cudaGetLastError());
+            cudaLaunchConfig_t rc_cfg = dependent_launch_config(tiles * parts, 256, stream);
+            SM100_CUDA_TRY(cudaLaunchKernelEx(&rc_cfg, streamk_reduce_kernel<T::BM, T::BN>, (const float *)workspace, static_cast<bf16 *>(Y), M, N,
+                                              p.num_m_blocks, p.num_n_blocks, p.group_n, p.num_k_blocks, grid / T::CG, parts, alpha));
         }
         if (T::SPLIT_K > 1) {
             const size_t mn = (size_t)M * N;
             size_t blocks = (mn / 8 + 255) / 256;
             const size_t cap = (size_t)dev->sm_count * 8;
             if (blocks > cap) blocks = cap;
-            splitk_reduce_kernel<T::SPLIT_K><<<(unsigned)blocks, 256, 0, stream>>>(workspace, static_cast<bf16 *>(Y), mn, alpha);
-            SM100_CUDA_TRY(cudaGetLastError());
+            cudaLaunchConfig_t rc_cfg = dependent_launch_config((unsigned)blocks, 256, stream);
+            SM100_CUDA_TRY(cudaLaunchKernelEx(&rc_cfg, splitk_reduce_kernel<T::SPLIT_K>, (const float *)workspace, static_cast<bf16 *>(Y), mn, alpha));
         }
         return GEMM_OK;
     }

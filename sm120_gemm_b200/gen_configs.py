@@ -6,7 +6,8 @@ shared-memory cap for the mma.sync kernel), re-derived for the tcgen05 design:
 
   dt       bf16 | fp8 | mxfp8 | w4a16 | w4a4
   bm       128 (one CTA) or 256 (CTA pair, cta_group::2); always 128*cg
-  bn       64 | 128 | 192 | 256      (UMMA N; two FP32 accumulator buffers need 2*bn <= 512 TMEM columns)
+  bn       multiple of 16 up to 256  (UMMA N; two FP32 accumulator buffers need 2*bn <= 512 TMEM columns;
+           the TMA-store epilogue needs a multiple of 64)
   bk       one 128-byte swizzle span of K per stage: 64 bf16, 128 fp8, 256 fp4 elements
   s        TMA ring stages, bounded by the 227 KB of shared memory one CTA may use
   cg       CTA group (1 | 2)
@@ -114,6 +115,10 @@ def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8")) -> list[Gemm
             for sk in (2, 4, 7, 8, 16):
                 s = min(max_stages(dt, bn, cg, sk, 0, max_smem), 8)
                 out.append(GemmConfig(dt, 128 * cg, bn, bk, s, cg, sk, 0, 0))
+        # tile widths that fill 148 SMs in one wave for the decode shapes (N = 4096 with 4 K slices, N = 28672)
+        out.append(GemmConfig(dt, 128, 112, bk, min(max_stages(dt, 112, 1, 4, 0, max_smem), 10), 1, 4, 0, 0))
+        for bn in (208, 224):
+            out.append(GemmConfig(dt, 128, bn, bk, min(max_stages(dt, bn, 1, 1, 0, max_smem), 10), 1, 1, 0, 0))
         # stream-K: every SM streams the same number of bytes whatever the tile count
         for cg, bn in ((1, 64), (1, 128), (1, 192), (1, 256), (2, 128), (2, 256)):
             s = min(max_stages(dt, bn, cg, 0, 0, max_smem), 10)
