@@ -71,8 +71,8 @@ typedef struct GemmArgs {
     const void *X;          /* activations, layout per dtype                               */
     const void *W;          /* weights, layout per dtype                                   */
     void *Y;                /* bf16 M x N                                                  */
-    const void *x_scale;    /* MXFP8 / W4A4: ue8m0 [M][K/32]; else NULL                    */
-    const void *w_scale;    /* MXFP8 / W4A4: ue8m0 [N][K/32]; W4A16: bf16 [N][K/group]     */
+    const void *x_scale;    /* MXFP8 / W4A4: ue8m0 scales of X, TILED (see below); else NULL */
+    const void *w_scale;    /* MXFP8 / W4A4: ue8m0 scales of W, TILED; W4A16: bf16 [N][K/group] */
     float x_scale_f;        /* FP8: per-tensor scale of X (1.0 elsewhere)                  */
     float w_scale_f;        /* FP8: per-tensor scale of W (1.0 elsewhere)                  */
     void *workspace;        /* split-K partial sums; may be NULL when not needed           */
@@ -82,6 +82,14 @@ typedef struct GemmArgs {
     gemm_stream_t stream;
 } GemmArgs;
 
+/*
+ * Scale layout of the MX data types.  One ue8m0 byte scales 32 consecutive K-elements of one
+ * row.  The kernels read the scales in 512-byte atoms of 128 rows x 4 K-blocks (what one
+ * tcgen05.cp moves into TMEM): atom (r/128, kb/4) at byte ((r/128) * ceil(K/128) + kb/4) * 512,
+ * and inside the atom row r, K-block kb at byte (r%32)*16 + ((r%128)/32)*4 + kb%4.  Rows are
+ * padded to a multiple of 128.  libsm100gemm_util.so converts a row-major [rows][K/32] array
+ * into this layout (include/sm100_gemm_util.h).  Weights are converted once; K must be a multiple of 128 (MXFP8) / 256 (W4A4).
+ */
 /* Returns GEMM_OK or an error code; asynchronous on success. */
 int gemm_run_ex(const GemmArgs *args);
 

@@ -222,7 +222,7 @@ _UTIL = None
 
 
 def util_lib() -> ctypes.CDLL:
-    """``libsm100gemm_util.so``: gemm_interleave_blocks, gemm_spacer (csrc/gemm_util.cu)."""
+    """``libsm100gemm_util.so``: gemm_interleave_blocks, gemm_spacer, gemm_mx_scales_to_tiled (csrc/gemm_util.cu)."""
     global _UTIL
     if _UTIL is None:
         path = os.path.join(KERNEL_DIR, "libsm100gemm_util.so")
@@ -234,6 +234,10 @@ def util_lib() -> ctypes.CDLL:
         lib.gemm_interleave_blocks.restype = ctypes.c_int
         lib.gemm_spacer.argtypes = [ctypes.c_uint, ctypes.c_void_p]
         lib.gemm_spacer.restype = ctypes.c_int
+        lib.gemm_mx_tiled_scale_bytes.argtypes = [ctypes.c_longlong, ctypes.c_int]
+        lib.gemm_mx_tiled_scale_bytes.restype = ctypes.c_size_t
+        lib.gemm_mx_scales_to_tiled.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p]
+        lib.gemm_mx_scales_to_tiled.restype = ctypes.c_int
         _UTIL = lib
     return _UTIL
 

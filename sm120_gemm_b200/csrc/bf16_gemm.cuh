@@ -38,7 +38,9 @@ using bf16 = __nv_bfloat16;
 
 namespace sm100 {
 
-enum : int { OPK_BF16 = 0, OPK_E4M3 = 1 };      // operand element kind of the dense kernel
+// operand element kind: bf16; e4m3 with per-tensor scales; e4m3 / e2m1 with one ue8m0 scale per 32
+// K-elements of both operands (block-scaled MMA, scale factors staged in TMEM)
+enum : int { OPK_BF16 = 0, OPK_E4M3 = 1, OPK_MXFP8 = 2, OPK_MXFP4 = 3 };
 enum : int { EPI_DIRECT = 0, EPI_TMA = 1 };     // epilogue: register->global stores, or smem + TMA store
 
 struct GemmParams {
@@ -51,6 +53,10 @@ struct GemmParams {
     float *workspace;     // split-K partial sums [split][M][N]
     float alpha;          // epilogue scale (FP8 per-tensor: sx*sw)
     uint32_t *status;
+    // block-scaled kinds: ue8m0 scale factors in 512-byte atoms of 128 rows x 4 K-blocks,
+    // atom (row/128, kblock/4) at byte ((row/128) * sf_k_atoms + kblock/4) * 512
+    const uint8_t *sf_x, *sf_w;
+    int sf_k_atoms;
 };
 
 // One piece of work for a CTA (or CTA pair): accumulate `kb_count` k-blocks of one output tile.
@@ -126,23 +132,35 @@ struct UmmaGemmTraits {
     static constexpr int CG = CG_;
     static constexpr int SPLIT_K = SPLIT_K_;
     static constexpr int EPI = (SPLIT_K_ > 1) ? EPI_DIRECT : EPI_;   // stream-K (0) keeps the chosen epilogue for whole tiles
-    static constexpr int ELEM_BYTES = (OPK_ == OPK_BF16) ? 2 : 1;
+    static constexpr int ELEM_BITS = (OPK_ == OPK_BF16) ? 16 : (OPK_ == OPK_MXFP4) ? 4 : 8;
+    static constexpr bool BLOCK_SCALED = (OPK_ == OPK_MXFP8 || OPK_ == OPK_MXFP4);
     static constexpr int BM_CTA = 128;                     // rows of X (and of the accumulator) per CTA
     static constexpr int BM = BM_CTA * CG_;                // rows of the tile
     static constexpr int BK_BYTES = 128;                   // one swizzle span per row
-    static constexpr int BK = BK_BYTES / ELEM_BYTES;       // K elements per stage
+    static constexpr int BK = BK_BYTES * 8 / ELEM_BITS;    // K elements per stage
+    static constexpr int BK_COORD = (OPK_ == OPK_BF16) ? BK : BK_BYTES;   // the same, in tensor-map elements (bf16, else bytes)
     static constexpr int UMMA_K_STEPS = BK_BYTES / 32;     // 4 MMAs per stage
     static constexpr int BN_CTA = BN_ / CG_;               // rows of W this CTA loads
     static constexpr int A_BYTES = BM_CTA * BK_BYTES;
     static constexpr int B_BYTES = BN_CTA * BK_BYTES;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    // block-scaled kinds: per stage, one 512-byte scale atom per 128 rows and 128 K-elements
+    static constexpr int SF_K_ATOMS = BLOCK_SCALED ? BK / 128 : 0;
+    static constexpr int SF_N_ATOMS = (BN_ + 127) / 128;
+    static constexpr int SF_A_BYTES = SF_K_ATOMS * 512;
+    static constexpr int SF_B_BYTES = SF_K_ATOMS * SF_N_ATOMS * 512;
+    static constexpr int SF_BYTES = SF_A_BYTES + SF_B_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;   // bytes that arrive per stage
     static constexpr int OUT_CHUNK = 64;                   // output columns per TMA store (128 bytes of bf16)
     static constexpr int STAGING_BYTES = (EPI == EPI_TMA) ? 2 * BM_CTA * OUT_CHUNK * 2 : 0;
     static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4;
-    static constexpr int SMEM_BYTES = STAGES_ * STAGE_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + 16;
+    static constexpr int SF_RING_BYTES = (STAGES_ * SF_BYTES + 1023) / 1024 * 1024;   // keeps the staging tiles 1024-byte aligned
+    static constexpr int SMEM_BYTES = STAGES_ * (A_BYTES + B_BYTES) + SF_RING_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + 16;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;   // slack to align the base to 1024 bytes
     static constexpr int ACC_STRIDE = (BN_ + 31) / 32 * 32;  // TMEM columns between the two accumulator buffers
-    static constexpr int ACC_COLS = 2 * ACC_STRIDE;        // two FP32 accumulator buffers
+    static constexpr int SF_COLS = SF_K_ATOMS * (1 + SF_N_ATOMS) * 4;   // TMEM columns of the staged scale factors
+    // two FP32 accumulator buffers when they fit beside the scale factors, else one
+    static constexpr int ACC_STAGES = (2 * ACC_STRIDE + SF_COLS <= 512) ? 2 : 1;
+    static constexpr int ACC_COLS = ACC_STAGES * ACC_STRIDE + SF_COLS;
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
     static constexpr int THREADS = 256;
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "BN (the UMMA N extent) is a multiple of 16 up to 256");
@@ -150,6 +168,8 @@ struct UmmaGemmTraits {
     static_assert((BN_ / CG_) % 8 == 0, "each CTA loads whole 8-row swizzle groups of W");
     static_assert(CG_ == 1 || CG_ == 2, "CTA group is 1 or 2");
     static_assert(STAGES_ >= 2, "at least two ring stages");
+    static_assert(!BLOCK_SCALED || (CG_ == 1 && BN_ % 128 == 0), "block-scaled tiles: one CTA, BN a multiple of the 128-row scale atom");
+    static_assert(ACC_COLS <= 512, "TMEM has 512 columns");
     static_assert(SMEM_ALLOC <= 232448, "exceeds the 227 KB of shared memory one CTA can have");
 };
 
@@ -169,7 +189,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
     const uint32_t a_base = smem_base;
     const uint32_t b_base = smem_base + STAGES * T::A_BYTES;
-    const uint32_t stg_base = b_base + STAGES * T::B_BYTES;
+    const uint32_t sf_base = b_base + STAGES * T::B_BYTES;
+    const uint32_t stg_base = sf_base + T::SF_RING_BYTES;
     const uint32_t bar_base = stg_base + T::STAGING_BYTES;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
@@ -244,11 +265,25 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     }
                     if (!ok) break;
                     for (int d = 0; d < nb_burst; d++) {
-                        const int kx = (kb0 + kb + d) * T::BK;
+                        const int kx = (kb0 + kb + d) * T::BK_COORD;
                         if constexpr (CG == 1) {
                             mbar_arrive_expect_tx(full_bar(stage), T::STAGE_BYTES);
                             tma_load_2d(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w);
                             tma_load_2d(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x);
+                            if constexpr (T::BLOCK_SCALED) {
+                                // scale atoms of this k-block: X rows first, then one per 128 W rows
+                                const uint32_t sf_dst = sf_base + stage * T::SF_BYTES;
+                                const size_t katom = (size_t)(kb0 + kb + d) * T::SF_K_ATOMS;
+#pragma unroll
+                                for (int a = 0; a < T::SF_K_ATOMS; a++) {
+                                    bulk_load(sf_dst + a * 512, p.sf_x + ((size_t)(row_x / 128) * p.sf_k_atoms + katom + a) * 512, 512,
+                                              full_bar(stage));
+#pragma unroll
+                                    for (int j = 0; j < T::SF_N_ATOMS; j++)
+                                        bulk_load(sf_dst + T::SF_A_BYTES + (a * T::SF_N_ATOMS + j) * 512,
+                                                  p.sf_w + ((size_t)(row_w / 128 + j) * p.sf_k_atoms + katom + a) * 512, 512, full_bar(stage));
+                                }
+                            }
                         } else {
                             if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
                             const uint32_t fb = full_leader + 8u * stage;
@@ -265,6 +300,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (lane == 0 && cta_rank == 0) {
             const uint32_t instr = (T::OPK == OPK_BF16) ? make_idesc(UMMA_BF16, UMMA_BF16, T::BM, BN)
                                                          : make_idesc(UMMA_E4M3, UMMA_E4M3, T::BM, BN);
+            // scale factors live behind the accumulator buffers: X atoms, then W atoms
+            const uint32_t sfa_tmem = tmem_base + (uint32_t)(T::ACC_STAGES * T::ACC_STRIDE);
+            const uint32_t sfb_tmem = sfa_tmem + (uint32_t)(T::SF_K_ATOMS * 4);
             int stage = 0;
             uint32_t phase = 0;
             int titer = 0;
@@ -272,8 +310,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
             WorkItem w;
             for (; ok && sched.next(w); titer++) {
-                const int acc = titer & 1;
-                const uint32_t acc_phase = (titer >> 1) & 1;
+                const int acc = titer % T::ACC_STAGES;
+                const uint32_t acc_phase = (titer / T::ACC_STAGES) & 1;
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, acc)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * T::ACC_STRIDE);
@@ -285,9 +323,30 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     tc_fence_after_sync();
                     const uint64_t a_desc = make_smem_desc_k128(a_base + stage * T::A_BYTES);
                     const uint64_t b_desc = make_smem_desc_k128(b_base + stage * T::B_BYTES);
+                    if constexpr (T::BLOCK_SCALED) {
+                        const uint32_t sf_src = sf_base + stage * T::SF_BYTES;
+#pragma unroll
+                        for (int a = 0; a < T::SF_K_ATOMS; a++) {
+                            tmem_cp_sf_atom(sfa_tmem + a * 4, make_sf_atom_desc(sf_src + a * 512));
+#pragma unroll
+                            for (int j = 0; j < T::SF_N_ATOMS; j++)
+                                tmem_cp_sf_atom(sfb_tmem + (a * T::SF_N_ATOMS + j) * 4,
+                                                make_sf_atom_desc(sf_src + T::SF_A_BYTES + (a * T::SF_N_ATOMS + j) * 512));
+                        }
+                    }
 #pragma unroll
                     for (int k = 0; k < T::UMMA_K_STEPS; k++) {
                         const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        if constexpr (T::OPK == OPK_MXFP8) {
+                            // 4 instructions of 32 K-elements share one atom: instruction k uses scale byte k
+                            umma_mxf8(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k),
+                                      make_idesc_block_scaled(UMMA_E4M3, UMMA_E4M3, T::BM, BN, k, k), sfa_tmem, sfb_tmem, accumulate);
+                        } else if constexpr (T::OPK == OPK_MXFP4) {
+                            // 4 instructions of 64 K-elements: two per atom, each using one half (2 scale bytes)
+                            umma_mxf4(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k),
+                                      make_idesc_block_scaled(UMMA_MXF4_E2M1, UMMA_MXF4_E2M1, T::BM, BN, (k & 1) * 2, (k & 1) * 2),
+                                      sfa_tmem + (k >> 1) * 4, sfb_tmem + (k >> 1) * (T::SF_N_ATOMS * 4), accumulate);
+                        } else
                         if constexpr (T::OPK == OPK_BF16)
                             umma_f16<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, accumulate);
                         else
@@ -315,8 +374,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             tile_to_mn(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
             const int m0 = mb * T::BM + (int)cta_rank * T::BM_CTA;
             const int n0 = nb * BN;
-            const int acc = titer & 1;
-            const uint32_t acc_phase = (titer >> 1) & 1;
+            const int acc = titer % T::ACC_STAGES;
+            const uint32_t acc_phase = (titer / T::ACC_STAGES) & 1;
             // all 128 epilogue threads must take the same decision, or the ones that go on would
             // wait at a named barrier for the ones that left
             const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, acc);
@@ -380,7 +439,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 #pragma unroll
                         for (int i = 0; i < 16; i++) {
                             float lo = __uint_as_float(r[2 * i]), hi = __uint_as_float(r[2 * i + 1]);
-                            if constexpr (T::OPK != OPK_BF16) { lo *= p.alpha; hi *= p.alpha; }
+                            if constexpr (T::OPK == OPK_E4M3) { lo *= p.alpha; hi *= p.alpha; }
                             pk[i] = pack_bf16x2(lo, hi);
                         }
 #pragma unroll
@@ -409,7 +468,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
                         float lo = __uint_as_float(r[2 * i]), hi = __uint_as_float(r[2 * i + 1]);
-                        if constexpr (T::OPK != OPK_BF16) { lo *= p.alpha; hi *= p.alpha; }
+                        if constexpr (T::OPK == OPK_E4M3) { lo *= p.alpha; hi *= p.alpha; }
                         pk[i] = pack_bf16x2(lo, hi);
                     }
                     if (grow < p.M) {
@@ -570,7 +629,8 @@ struct UmmaGemmLauncher {
     static bool can_run(int M, int N, int K)
     {
         if (M <= 0 || N <= 0 || K <= 0) return false;
-        if ((K * T::ELEM_BYTES) % 16 != 0 || N % 8 != 0) return false;   // 16-byte row pitches
+        if (((long long)K * T::ELEM_BITS) % 128 != 0 || N % 8 != 0) return false;   // 16-byte row pitches
+        if (T::BLOCK_SCALED && K % T::BK != 0) return false;               // whole scale atoms along K
         if (T::SPLIT_K > 1) {
             int kb = (K + T::BK - 1) / T::BK;
             if (K % T::BK != 0 || kb % T::SPLIT_K != 0) return false;     // equal, non-empty K slices
@@ -624,10 +684,13 @@ struct UmmaGemmLauncher {
     }
 
     static int run(int M, int N, int K, const void *X, const void *W, void *Y, float *workspace, size_t workspace_bytes_given,
-                   float alpha, int sm_limit, cudaStream_t stream)
+                   float alpha, int sm_limit, cudaStream_t stream, const void *sf_x = nullptr, const void *sf_w = nullptr)
     {
         if (!can_run(M, N, K)) return set_error(GEMM_ERR_SHAPE, "shape %dx%dx%d not supported by this configuration", M, N, K);
         if (!X || !W || !Y) return set_error(GEMM_ERR_ARG, "null operand pointer");
+        if (T::BLOCK_SCALED && (!sf_x || !sf_w)) return set_error(GEMM_ERR_ARG, "block-scaled configuration needs x_scale and w_scale");
+        if (T::BLOCK_SCALED && ((reinterpret_cast<uintptr_t>(sf_x) | reinterpret_cast<uintptr_t>(sf_w)) & 15u))
+            return set_error(GEMM_ERR_ARG, "scale arrays must be 16-byte aligned");
         if (T::SPLIT_K != 1) {
             if (!workspace) return set_error(GEMM_ERR_WORKSPACE, "split-K configuration needs a workspace");
             if (workspace_bytes_given != 0 && workspace_bytes_given < workspace_bytes(M, N, K))
@@ -650,9 +713,11 @@ struct UmmaGemmLauncher {
 
         const CUtensorMapDataType dt = (T::OPK == OPK_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
         CUtensorMap tx, tw, ty;
-        rc = make_tmap_2d(&tx, dt, X, (uint64_t)K, (uint64_t)M, (uint64_t)K * T::ELEM_BYTES, T::BK, T::BM_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
+        const uint64_t row_bytes = (uint64_t)K * T::ELEM_BITS / 8;
+        const uint64_t row_elems = (T::OPK == OPK_BF16) ? (uint64_t)K : row_bytes;   // fp8 / packed fp4 rows are mapped as bytes
+        rc = make_tmap_2d(&tx, dt, X, row_elems, (uint64_t)M, row_bytes, T::BK_COORD, T::BM_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != GEMM_OK) return rc;
-        rc = make_tmap_2d(&tw, dt, W, (uint64_t)K, (uint64_t)N, (uint64_t)K * T::ELEM_BYTES, T::BK, T::BN_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = make_tmap_2d(&tw, dt, W, row_elems, (uint64_t)N, row_bytes, T::BK_COORD, T::BN_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != GEMM_OK) return rc;
         if (T::EPI == EPI_TMA) {
             rc = make_tmap_2d(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, Y, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, T::OUT_CHUNK, T::BM_CTA,
@@ -673,6 +738,9 @@ struct UmmaGemmLauncher {
         p.workspace = workspace;
         p.alpha = alpha;
         p.status = dev->status;
+        p.sf_x = static_cast<const uint8_t *>(sf_x);
+        p.sf_w = static_cast<const uint8_t *>(sf_w);
+        p.sf_k_atoms = (K + 127) / 128;
         const long long work = (long long)p.num_m_blocks * p.num_n_blocks * (T::SPLIT_K > 0 ? T::SPLIT_K : p.num_k_blocks);
         int grid = 0;
         rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &grid);

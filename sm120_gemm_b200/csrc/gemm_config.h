@@ -73,6 +73,7 @@ struct GemmConfig {
     {
         if (M <= 0 || N <= 0 || K <= 0) return false;
         if (((long long)K * sm100::elem_bits(dt)) % 128 != 0 || N % 8 != 0) return false;
+        if ((dt == GEMM_DT_MXFP8 || dt == GEMM_DT_W4A4) && K % bk != 0) return false;
         if (split_k > 1 && (K % bk != 0 || (K / bk) % split_k != 0)) return false;
         return true;
     }
@@ -81,10 +82,12 @@ struct GemmConfig {
     // a plugin reports the exact figure through gemm_smem_bytes()).
     size_t smem_bytes() const
     {
+        const size_t k_atoms = (dt == GEMM_DT_MXFP8 || dt == GEMM_DT_W4A4) ? bk / 128 : 0;   // 512-byte scale atoms per stage
+        const size_t sf_ring = (num_stages * k_atoms * (1 + (bn + 127) / 128) * 512 + 1023) / 1024 * 1024;
         const size_t a = 128 * 128, b = (size_t)(bn / cg) * 128;
         const size_t staging = (split_k <= 1 && epi == 1) ? 2 * 128 * 64 * 2 : 0;
         const size_t barriers = (2 * (size_t)num_stages + 4) * 8 + 16;
-        return num_stages * (a + b) + staging + barriers + 1024;
+        return num_stages * (a + b) + sf_ring + staging + barriers + 1024;
     }
 };
 

@@ -3,6 +3,7 @@
 // the idle spacer kernel of the timing protocol.  No counterpart in the reference, which is
 // single-GPU (device 0 is hard-coded, src/bf16_gemm.cuh:531).
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 
 namespace {
@@ -23,6 +24,23 @@ __global__ void __launch_bounds__(256) interleave_blocks_kernel(const uint4 *__r
     }
 }
 
+// Row-major ue8m0 scales [rows][kblocks] (one per 32 K-elements) -> the atom layout the
+// block-scaled kernels read: 512-byte atoms of 128 rows x 4 K-blocks, atom (r/128, kb/4) at
+// byte ((r/128)*k_atoms + kb/4)*512, and inside an atom byte (r%32)*16 + ((r%128)/32)*4 + kb%4
+// (32 rows of 16 bytes: what one tcgen05.cp moves into TMEM).  Padding rows / K-blocks get the
+// scale 1.0 (127); they only ever multiply zero-filled operand data.
+__global__ void __launch_bounds__(256) mx_scales_to_tiled_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                                                  long long rows, int kblocks, int k_atoms, long long total)
+{
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long atom = i >> 9;
+        const int in = (int)(i & 511);
+        const long long r = (atom / k_atoms) * 128 + ((in >> 2) & 3) * 32 + (in >> 4);
+        const int kb = (int)(atom % k_atoms) * 4 + (in & 3);
+        dst[i] = (r < rows && kb < kblocks) ? src[r * kblocks + kb] : (uint8_t)127;
+    }
+}
+
 __global__ void spacer_kernel(unsigned us) { __nanosleep(us * 1000u); }
 
 }  // namespace
@@ -39,6 +57,26 @@ int gemm_interleave_blocks(const void *blocked, void *Y, int g, long long M, int
     if (blocks > 148 * 16) blocks = 148 * 16;
     interleave_blocks_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4 *>(blocked), static_cast<uint4 *>(Y), g, M, nb_vec);
+    return (int)cudaGetLastError();
+}
+
+// Bytes of the tiled scale array for `rows` rows and K elements (K a multiple of 32).
+size_t gemm_mx_tiled_scale_bytes(long long rows, int K)
+{
+    const long long k_atoms = ((long long)K / 32 + 3) / 4;
+    return (size_t)((rows + 127) / 128 * k_atoms * 512);
+}
+
+// src: row-major [rows][K/32] ue8m0; dst: gemm_mx_tiled_scale_bytes(rows, K) bytes, 16-byte aligned.
+int gemm_mx_scales_to_tiled(const void *src, void *dst, long long rows, int K, void *stream)
+{
+    if (rows <= 0 || K <= 0 || K % 32 != 0) return (int)cudaErrorInvalidValue;
+    const int kblocks = K / 32, k_atoms = (kblocks + 3) / 4;
+    const long long total = (rows + 127) / 128 * k_atoms * 512;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    mx_scales_to_tiled_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), rows, kblocks, k_atoms, total);
     return (int)cudaGetLastError();
 }
 

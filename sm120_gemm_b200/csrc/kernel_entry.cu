@@ -22,10 +22,12 @@ constexpr int AB = GEMM_AB;
 constexpr int EPI = GEMM_EPI;
 constexpr int BM = 128 * CG;
 
-static_assert(DT == GEMM_DT_BF16 || DT == GEMM_DT_FP8, "this entry file builds the dense bf16 / fp8 kernels");
-static_assert(AB == 0, "operand swap is not part of the dense kernel");
+static_assert(DT == GEMM_DT_BF16 || DT == GEMM_DT_FP8 || DT == GEMM_DT_MXFP8 || DT == GEMM_DT_W4A4,
+              "this entry file builds the bf16, fp8, mxfp8 and mx-fp4 kernels");
+static_assert(AB == 0, "operand swap is not part of this kernel");
 
-using Traits = sm100::UmmaGemmTraits<DT == GEMM_DT_BF16 ? sm100::OPK_BF16 : sm100::OPK_E4M3, BN, STAGES, CG, SK, EPI>;
+constexpr int OPK = DT == GEMM_DT_BF16 ? sm100::OPK_BF16 : DT == GEMM_DT_FP8 ? sm100::OPK_E4M3 : DT == GEMM_DT_MXFP8 ? sm100::OPK_MXFP8 : sm100::OPK_MXFP4;
+using Traits = sm100::UmmaGemmTraits<OPK, BN, STAGES, CG, SK, EPI>;
 using Launcher = sm100::UmmaGemmLauncher<Traits>;
 
 #define GEMM_STR2(x) #x
@@ -64,7 +66,7 @@ int gemm_run_ex(const GemmArgs *a)
     if ((int)a->dtype != DT) return sm100::set_error(GEMM_ERR_ARG, "dtype %u does not match plugin %s", a->dtype, kConfigName);
     const float alpha = (DT == GEMM_DT_FP8) ? a->x_scale_f * a->w_scale_f : 1.0f;
     return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, static_cast<float *>(a->workspace), a->workspace_bytes, alpha,
-                         a->sm_limit, a->stream);
+                         a->sm_limit, a->stream, a->x_scale, a->w_scale);
 }
 
 const char *gemm_config_name(void) { return kConfigName; }

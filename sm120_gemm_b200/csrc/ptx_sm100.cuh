@@ -280,6 +280,46 @@ __device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, ui
             : "memory");
 }
 
+// Block-scaled MMAs (one CTA): D (+)= (A * SFA) * (B * SFB), ue8m0 scale factors read from TMEM.
+// mxf8f6f4: one scale per 32 K-elements, 32 K-elements per instruction (scale_vec::1X).
+__device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                          uint32_t sfb_tmem, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
+
+// mxf4: e2m1 elements, one scale per 32 K-elements, 64 K-elements per instruction (scale_vec::2X).
+__device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                          uint32_t sfb_tmem, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
+
+// Shared memory -> TMEM copy of one 512-byte scale-factor atom: 32 rows x 16 bytes, written
+// to 4 TMEM columns of lanes 0..31 and replicated into the other three lane quarters (the
+// form the block-scaled MMA reads).  Issued by one thread, ordered with its later MMAs.
+__device__ __forceinline__ void tmem_cp_sf_atom(uint32_t taddr, uint64_t smem_desc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
+// Untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), completion counted
+// on an mbarrier of this CTA.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 // Arrive once on `bar` (this CTA) when every tcgen05.mma issued so far by this thread is done.
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {

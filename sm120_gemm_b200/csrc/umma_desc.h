@@ -36,6 +36,18 @@ UMMA_HD uint64_t make_smem_desc_k128(uint32_t smem_addr)
     return d;
 }
 
+// One 512-byte scale-factor atom for tcgen05.cp 32x128b: 32 rows of 16 bytes, no swizzle.
+// Eight 16-byte rows form a 128-byte core matrix, so 8-row groups are 128 bytes apart (SBO);
+// the copy is a single 16-byte column wide, so the leading-dimension offset is unused.
+UMMA_HD uint64_t make_sf_atom_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)(128u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;   // swizzle mode 0
+}
+
 // Stepping along K inside the 128-byte span: the start address moves by the byte width of
 // one MMA's K extent (32 bytes for every operand type: 16 bf16 / 32 fp8 / 64 fp4).
 UMMA_HD uint64_t advance_desc_k(uint64_t desc, uint32_t k_step)
@@ -47,7 +59,8 @@ UMMA_HD uint64_t advance_desc_k(uint64_t desc, uint32_t k_step)
 //  [4,6) D format (1 = F32)   [7,10) A format   [10,13) B format   [15] A major   [16] B major
 //  [17,23) N >> 3             [24,29) M >> 4    (major 0 = K-major)
 enum : uint32_t { UMMA_F16 = 0, UMMA_BF16 = 1, UMMA_TF32 = 2 };                        // kind::f16 / tf32
-enum : uint32_t { UMMA_E4M3 = 0, UMMA_E5M2 = 1, UMMA_E2M3 = 3, UMMA_E3M2 = 4, UMMA_E2M1 = 5 };  // kind::f8f6f4
+enum : uint32_t { UMMA_E4M3 = 0, UMMA_E5M2 = 1, UMMA_E2M3 = 3, UMMA_E3M2 = 4, UMMA_E2M1 = 5 };  // kind::f8f6f4 / mxf8f6f4
+enum : uint32_t { UMMA_MXF4_E2M1 = 1 };                                                  // kind::mxf4
 
 UMMA_HD uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt, int M, int N)
 {

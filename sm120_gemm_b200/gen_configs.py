@@ -64,16 +64,22 @@ class GemmConfig:
         """Dynamic shared memory of the dense kernel; must equal UmmaGemmTraits::SMEM_ALLOC."""
         a = 128 * 128
         b = (self.bn // self.cg) * 128
+        # block-scaled kinds stage one 512-byte scale atom per 128 rows and 128 K-elements
+        k_atoms = self.bk // 128 if self.dt in ("mxfp8", "w4a4") else 0
+        sf = k_atoms * (1 + -(-self.bn // 128)) * 512
         epi = 0 if self.split_k > 1 else self.epi
         staging = 2 * 128 * 64 * 2 if epi == 1 else 0
         barriers = (2 * self.num_stages + 4) * 8 + 16
-        return self.num_stages * (a + b) + staging + barriers + 1024
+        sf_ring = -(-self.num_stages * sf // 1024) * 1024
+        return self.num_stages * (a + b) + sf_ring + staging + barriers + 1024
 
     def is_valid_for(self, M: int, N: int, K: int) -> bool:
         """The plugin's own gemm_can_run, restated (reference: src/gemm_config.h:34-38)."""
         if M <= 0 or N <= 0 or K <= 0:
             return False
         if (K * ELEM_BITS[self.dt]) % 128 != 0 or N % 8 != 0:
+            return False
+        if self.dt in ("mxfp8", "w4a4") and K % self.bk != 0:
             return False
         if self.split_k > 1:
             if K % self.bk != 0 or (K // self.bk) % self.split_k != 0:
@@ -94,11 +100,26 @@ def max_stages(dt: str, bn: int, cg: int, sk: int, epi: int, cap: int = MAX_SMEM
     return s
 
 
-def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8")) -> list[GemmConfig]:
+def generate_block_scaled(dt: str, max_smem: int) -> list[GemmConfig]:
+    """MXFP8 / MX-FP4: one CTA per tile, BN a multiple of the 128-row scale atom."""
+    bk = 128 * 8 // ELEM_BITS[dt]
+    out = []
+    for bn in (128, 256):
+        for epi in (1, 0):
+            out.append(GemmConfig(dt, 128, bn, bk, min(max_stages(dt, bn, 1, 1, epi, max_smem), 8), 1, 1, 0, epi))
+        for sk in (2, 4, 0):
+            out.append(GemmConfig(dt, 128, bn, bk, min(max_stages(dt, bn, 1, sk, 0, max_smem), 8), 1, sk, 0, 0))
+    return out
+
+
+def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8", "mxfp8", "w4a4")) -> list[GemmConfig]:
     out: list[GemmConfig] = []
     for dt in dts:
+        if dt in ("mxfp8", "w4a4"):
+            out += generate_block_scaled(dt, max_smem)
+            continue
         if dt not in ("bf16", "fp8"):
-            continue  # the block-scaled and W4A16 kernels have their own generators
+            continue  # W4A16 has its own kernel and generator
         bk = 128 * 8 // ELEM_BITS[dt]
         for cg in (1, 2):
             for bn in (64, 128, 192, 256):
@@ -129,7 +150,7 @@ def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8")) -> list[Gemm
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--max-smem-kb", type=int, default=MAX_SMEM // 1024)
-    ap.add_argument("--dt", default="bf16,fp8")
+    ap.add_argument("--dt", default="bf16,fp8,mxfp8,w4a4")
     args = ap.parse_args()
     for c in generate_configs(args.max_smem_kb * 1024, tuple(args.dt.split(","))):
         print(c.name())

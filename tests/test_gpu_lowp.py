@@ -55,3 +55,88 @@ def test_fp8_8192_sampled_rows(registry, cuda_device):
     ref = o.gemm_f32(dx, dw)
     r = o.check_dense(to_bits(Y[torch.from_numpy(rows).cuda()]), ref, K, float(np.abs(dx).max()), float(np.abs(dw).max()))
     assert r["max_abs_err"] <= r["bound"] and r["frac_within_bf16_rounding"] >= 0.999, r
+
+
+def tiled_scales_numpy(sc: np.ndarray) -> np.ndarray:
+    """The atom layout of include/sm100_gemm.h, computed independently of the device converter."""
+    R, KB = sc.shape
+    ka = (KB + 3) // 4
+    out = np.full(((R + 127) // 128) * ka * 512, 127, np.uint8)
+    r = np.arange(R)[:, None]
+    kb = np.arange(KB)[None, :]
+    idx = ((r // 128) * ka + kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4
+    out[idx.ravel()] = sc.ravel()
+    return out
+
+
+def to_tiled_dev(sc: np.ndarray, K: int) -> torch.Tensor:
+    import sm120_gemm_b200 as g
+
+    util = g.util_lib()
+    src = torch.from_numpy(np.ascontiguousarray(sc)).cuda()
+    dst = torch.empty(util.gemm_mx_tiled_scale_bytes(sc.shape[0], K), dtype=torch.uint8, device="cuda")
+    assert util.gemm_mx_scales_to_tiled(src.data_ptr(), dst.data_ptr(), sc.shape[0], K, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    return dst
+
+
+def test_scale_tiling_kernel(cuda_device):
+    rng = np.random.default_rng(5)
+    for (R, K) in [(128, 128), (100, 256), (300, 1024), (257, 96 * 32)]:
+        sc = rng.integers(100, 140, (R, K // 32)).astype(np.uint8)
+        assert np.array_equal(to_tiled_dev(sc, K).cpu().numpy(), tiled_scales_numpy(sc))
+
+
+def mx_case(M, N, K, kind, seed, spread=True):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = rng.standard_normal((N, K)).astype(np.float32)
+    if spread:   # give the blocks different magnitudes so that wrong scale placement cannot hide
+        x *= np.exp2(rng.integers(-3, 4, (M, K // 32))).repeat(32, axis=1).astype(np.float32)
+        w *= np.exp2(rng.integers(-3, 4, (N, K // 32))).repeat(32, axis=1).astype(np.float32)
+    qx, sx = o.mx_quantise(x, kind)
+    qw, sw = o.mx_quantise(w, kind)
+    return qx, sx, qw, sw
+
+
+def run_mx(k, M, N, K, qx, sx, qw, sw):
+    return run_ex(k, M, N, K, torch.from_numpy(qx).cuda(), torch.from_numpy(qw).cuda(), x_scale=to_tiled_dev(sx, K),
+                  w_scale=to_tiled_dev(sw, K))
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 128), (128, 256, 256), (256, 512, 1024), (100, 136, 512), (1024, 1024, 1024)])
+def test_mxfp8(registry, cuda_device, shape):
+    """BASELINE config 4(b): e4m3 elements, ue8m0 scale per 32 K-elements on both operands."""
+    M, N, K = shape
+    qx, sx, qw, sw = mx_case(M, N, K, 8, seed=3)
+    dx, dw = o.mx_dequantise(qx, sx, 8), o.mx_dequantise(qw, sw, 8)
+    ref = o.gemm_f32(dx, dw)
+    ran = 0
+    for k in registry.kernels:
+        if k.config.dt != "mxfp8" or not k.can_run(M, N, K):
+            continue
+        Y = to_bits(run_mx(k, M, N, K, qx, sx, qw, sw))
+        assert not np.isnan(o.bf16_bits_to_f32(Y)).any(), k.config.name()
+        r = o.check_dense(Y, ref, K, float(np.abs(dx).max()), float(np.abs(dw).max()))
+        assert r["ok"], (k.config.name(), r)
+        ran += 1
+    assert ran >= 5
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 256), (128, 256, 512), (16, 512, 1024), (1, 256, 2048), (100, 136, 512), (512, 1024, 2048)])
+def test_w4a4_mxfp4(registry, cuda_device, shape):
+    """BASELINE config 5(b): e2m1 elements (two per byte), ue8m0 scale per 32 K-elements."""
+    M, N, K = shape
+    qx, sx, qw, sw = mx_case(M, N, K, 4, seed=4)
+    dx, dw = o.mx_dequantise(qx, sx, 4), o.mx_dequantise(qw, sw, 4)
+    ref = o.gemm_f32(dx, dw)
+    ran = 0
+    for k in registry.kernels:
+        if k.config.dt != "w4a4" or not k.can_run(M, N, K):
+            continue
+        Y = to_bits(run_mx(k, M, N, K, qx, sx, qw, sw))
+        assert not np.isnan(o.bf16_bits_to_f32(Y)).any(), k.config.name()
+        r = o.check_quantised(Y, ref)
+        assert r["ok"], (k.config.name(), r)
+        ran += 1
+    assert ran >= 5

@@ -46,6 +46,17 @@ def test_registry_loads_every_plugin_and_symbol(registry):
         assert k.smem_bytes() == k.config.smem_bytes()
 
 
+def test_util_library_exports_its_header():
+    header = open(os.path.join(ROOT, "include", "sm100_gemm_util.h")).read()
+    declared = set(re.findall(r"\b(gemm_[a-z_]+)\s*\(", header))
+    assert declared == {"gemm_interleave_blocks", "gemm_spacer", "gemm_mx_tiled_scale_bytes", "gemm_mx_scales_to_tiled"}
+    lib = g.util_lib()
+    for sym in declared:
+        assert getattr(lib, sym) is not None
+    assert lib.gemm_mx_tiled_scale_bytes(100, 256) == 1 * 2 * 512      # one 128-row tile, two 4-block atoms
+    assert lib.gemm_mx_tiled_scale_bytes(129, 128) == 2 * 1 * 512
+
+
 def test_validity_rules_match_plugins(registry):
     shapes = [(1, 8, 8), (128, 128, 64), (100, 136, 200), (128, 130, 64), (128, 128, 60), (128, 4096, 14336),
               (128, 4096, 14400), (16, 28672, 8192), (0, 8, 8), (1024, 1024, 1000)]
