@@ -72,6 +72,7 @@ struct GemmConfig {
     bool is_valid_for(int M, int N, int K) const
     {
         if (M <= 0 || N <= 0 || K <= 0) return false;
+        if (dt == GEMM_DT_W4A16) return M <= bn && N % 8 == 0 && K % 128 == 0;   // decode kernel, bn = padded M
         if (((long long)K * sm100::elem_bits(dt)) % 128 != 0 || N % 8 != 0) return false;
         if ((dt == GEMM_DT_MXFP8 || dt == GEMM_DT_W4A4) && K % bk != 0) return false;
         if (split_k > 1 && (K % bk != 0 || (K / bk) % split_k != 0)) return false;
@@ -82,6 +83,10 @@ struct GemmConfig {
     // a plugin reports the exact figure through gemm_smem_bytes()).
     size_t smem_bytes() const
     {
+        if (dt == GEMM_DT_W4A16) {   // bf16 tile + activation tile (1 KB granules) + packed int4 tile per stage
+            const size_t x = ((size_t)bn * 128 + 1023) / 1024 * 1024;
+            return num_stages * (128 * 128 + x + 128 * 32) + (3 * (size_t)num_stages + 4) * 8 + 16 + 1024;
+        }
         const size_t k_atoms = (dt == GEMM_DT_MXFP8 || dt == GEMM_DT_W4A4) ? bk / 128 : 0;   // 512-byte scale atoms per stage
         const size_t sf_ring = (num_stages * k_atoms * (1 + (bn + 127) / 128) * 512 + 1023) / 1024 * 1024;
         const size_t a = 128 * 128, b = (size_t)(bn / cg) * 128;

@@ -6,6 +6,7 @@
 //   -DGEMM_DT=<0..4> -DGEMM_BN=<64|128|192|256> -DGEMM_STAGES=<n> -DGEMM_CG=<1|2>
 //   -DGEMM_SK=<split-K> -DGEMM_AB=<0|1 operand swap> -DGEMM_EPI=<0|1>
 #include "bf16_gemm.cuh"
+#include "w4a16_gemm.cuh"
 
 #ifndef GEMM_DT
 #error "configuration macros missing: build through sm120_gemm_b200/build.py"
@@ -22,13 +23,17 @@ constexpr int AB = GEMM_AB;
 constexpr int EPI = GEMM_EPI;
 constexpr int BM = 128 * CG;
 
-static_assert(DT == GEMM_DT_BF16 || DT == GEMM_DT_FP8 || DT == GEMM_DT_MXFP8 || DT == GEMM_DT_W4A4,
-              "this entry file builds the bf16, fp8, mxfp8 and mx-fp4 kernels");
+#if GEMM_DT == 3
+// W4A16: operands swapped (AB = 1), BN is M padded, work is always cut stream-K fashion (SK = 0)
+static_assert(AB == 1 && SK == 0 && CG == 1 && EPI == 0, "W4A16 plugins are <dt>_bm128_bn<MPAD>_bk64_s<S>_cg1_sk0_ab1_e0");
+using Traits = sm100::W4A16Traits<BN, STAGES>;
+using Launcher = sm100::W4A16Launcher<Traits>;
+#else
 static_assert(AB == 0, "operand swap is not part of this kernel");
-
 constexpr int OPK = DT == GEMM_DT_BF16 ? sm100::OPK_BF16 : DT == GEMM_DT_FP8 ? sm100::OPK_E4M3 : DT == GEMM_DT_MXFP8 ? sm100::OPK_MXFP8 : sm100::OPK_MXFP4;
 using Traits = sm100::UmmaGemmTraits<OPK, BN, STAGES, CG, SK, EPI>;
 using Launcher = sm100::UmmaGemmLauncher<Traits>;
+#endif
 
 #define GEMM_STR2(x) #x
 #define GEMM_STR(x) GEMM_STR2(x)
@@ -56,7 +61,9 @@ void gemm_run(int M, int N, int K, const void *X, const void *W, void *Y, float 
         sm100::set_error(GEMM_ERR_ARG, "gemm_run takes bf16 operands; %s needs gemm_run_ex", kConfigName);
         return;
     }
+#if GEMM_DT != 3
     Launcher::run(M, N, K, X, W, Y, workspace, 0, 1.0f, 0, stream);
+#endif
 }
 
 int gemm_run_ex(const GemmArgs *a)
@@ -64,9 +71,14 @@ int gemm_run_ex(const GemmArgs *a)
     sm100::clear_error();
     if (!a || a->struct_size != sizeof(GemmArgs)) return sm100::set_error(GEMM_ERR_ARG, "GemmArgs is null or has the wrong struct_size");
     if ((int)a->dtype != DT) return sm100::set_error(GEMM_ERR_ARG, "dtype %u does not match plugin %s", a->dtype, kConfigName);
+#if GEMM_DT == 3
+    return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, a->w_scale, a->group_size, static_cast<float *>(a->workspace), a->workspace_bytes,
+                         a->sm_limit, a->stream);
+#else
     const float alpha = (DT == GEMM_DT_FP8) ? a->x_scale_f * a->w_scale_f : 1.0f;
     return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, static_cast<float *>(a->workspace), a->workspace_bytes, alpha,
                          a->sm_limit, a->stream, a->x_scale, a->w_scale);
+#endif
 }
 
 const char *gemm_config_name(void) { return kConfigName; }

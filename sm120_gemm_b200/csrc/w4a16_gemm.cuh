@@ -1,0 +1,335 @@
+// W4A16 for decode shapes (M <= 128): Y = X * dequant(W)^T with W signed int4 (two per byte
+// along K, low nibble = even k) and one bf16 scale per 128 K-elements of each weight row.
+// The reference has no quantised path; this kernel has no counterpart there.
+//
+// Operands are swapped: the 128 weight rows of a tile are the MMA's A operand (one TMEM lane
+// per weight row n) and the activations are the B operand (UMMA N = M padded to MPAD), so the
+// tensor work scales with M, not with a padded 128, and -- the point of the design -- the
+// group scale s[n][g] is a per-LANE scalar.  Weights are dequantised in shared memory to bf16
+// holding the EXACT integers -8..7; each 128-element group is multiplied out on the tensor core
+// into its own TMEM buffer and folded into per-thread FP32 totals as total[m] += s[n][g] * acc[m].
+// (Folding the scale into a bf16 weight instead, bf16(q*s), rounds every weight and misses
+// the 1e-3 accuracy bar.)
+//
+// Warps (384 threads):  0 TMA producer | 1 MMA issuer | 2 TMEM alloc | 3 idle
+//                       4-7  dequantisers: thread r converts row r of the tile (64 weights per k-block)
+//                       8-11 fold + epilogue: thread r owns weight row r (TMEM lane r)
+// Barriers per ring stage: landed[s] (TMA bytes: packed weights + activations) -> dequantisers;
+//   ready[s] (bf16 tile written) -> MMA; empty[s] (tcgen05.commit) -> producer.
+// Per group buffer b (2): gfull[b] (commit after the group's 2nd k-block) -> fold; gempty[b] -> MMA.
+//
+// Work is cut stream-K fashion in units of one group: every CTA gets the same number of
+// groups; a range that does not cover a tile's whole K leaves an FP32 partial [m][128] in the
+// CTA's slot, summed by streamk_reduce_kernel<128,128>.
+#pragma once
+#include "bf16_gemm.cuh"
+
+namespace sm100 {
+
+struct W4A16Params {
+    int M, N, K;
+    int num_n_tiles;
+    int num_groups;          // K / 128
+    bf16 *Y;
+    float *workspace;        // stream-K slots: [2 * grid][128 (m)][128 (n)] FP32
+    const bf16 *scales;      // [N][K/128]
+    uint32_t *status;
+};
+
+template <int MPAD_, int STAGES_>
+struct W4A16Traits {
+    static constexpr int MPAD = MPAD_;                 // UMMA N: M rounded up (16, 32, 64 or 128)
+    static constexpr int STAGES = STAGES_;
+    static constexpr int TILE_N = 128;                 // weight rows per tile = TMEM lanes
+    static constexpr int BK = 64;                      // K elements per ring stage (128 bytes of bf16)
+    static constexpr int GROUP_KB = 2;                 // k-blocks per scale group (128 / 64)
+    static constexpr int PACKED_BYTES = TILE_N * BK / 2;   // 4 KB of int4
+    static constexpr int X_BYTES = MPAD_ * 128;
+    static constexpr int A_BYTES = TILE_N * 128;       // dequantised bf16 tile
+    static constexpr int STAGE_SMEM = A_BYTES + ((X_BYTES + 1023) / 1024 * 1024) + PACKED_BYTES;
+    static constexpr int X_STRIDE = (X_BYTES + 1023) / 1024 * 1024;
+    static constexpr int NUM_BARRIERS = 3 * STAGES_ + 4;
+    static constexpr int SMEM_BYTES = STAGES_ * STAGE_SMEM + NUM_BARRIERS * 8 + 16;
+    static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
+    static constexpr int TMEM_COLS = 2 * MPAD_ <= 32 ? 32 : 2 * MPAD_ <= 64 ? 64 : 2 * MPAD_ <= 128 ? 128 : 256;
+    static constexpr int THREADS = 384;
+    static_assert(MPAD_ == 16 || MPAD_ == 32 || MPAD_ == 64 || MPAD_ == 128, "padded M is 16, 32, 64 or 128");
+    static_assert(SMEM_ALLOC <= 232448, "exceeds the shared memory of one CTA");
+};
+
+// 8 signed int4 (two's complement nibbles, nibble j = element j) -> four bf16x2 holding the exact
+// integers.  Flipping each nibble's top bit turns it into q+8 in 0..15; OR-ing that into the
+// mantissa of 128.0 (0x4300) gives the bf16 number 128+(q+8) exactly, and subtracting 136 leaves q.
+__device__ __forceinline__ void int4x8_to_bf16x8(uint32_t w, uint32_t (&out)[4])
+{
+    const uint32_t x = w ^ 0x88888888u;
+    const uint32_t x4 = x >> 4;
+    const uint32_t bias = 0x43084308u;   // bf16x2 {136, 136}
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        // byte j of x -> bits [0,8), byte j of x4 -> bits [16,24): low halves hold nibbles 2j and 2j+1
+        uint32_t sel = 0x4040u | (uint32_t)j | ((uint32_t)(4 + j) << 8);   // bytes: [j of x, 0-filler, j of x4, filler]
+        uint32_t y;
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(y) : "r"(x), "r"(x4), "r"(sel));
+        y = (y & 0x000f000fu) | 0x43004300u;
+        asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(out[j]) : "r"(y), "r"(bias));
+    }
+}
+
+template <class T>
+__global__ void __launch_bounds__(384, 1)
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const W4A16Params p)
+{
+    constexpr int STAGES = T::STAGES;
+    constexpr int MPAD = T::MPAD;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (smem_base - raw_addr);
+    const uint32_t a_base = smem_base;                                   // bf16 weight tiles
+    const uint32_t x_base = a_base + STAGES * T::A_BYTES;                // activation tiles
+    const uint32_t pk_base = x_base + STAGES * T::X_STRIDE;              // packed int4 tiles
+    const uint32_t bar_base = pk_base + STAGES * T::PACKED_BYTES;
+    auto landed_bar = [&](int s) { return bar_base + 8u * s; };
+    auto ready_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+    auto gfull_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + b); };
+    auto gempty_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 + b); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (bar_base - smem_base) + 8u * T::NUM_BARRIERS);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    const uint8_t *pk_ptr = smem + (pk_base - smem_base);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int cta = blockIdx.x, num_ctas = gridDim.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(landed_bar(s), 1);
+            mbar_init(ready_bar(s), 4);      // one arrival per dequantiser warp
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(gfull_bar(b), 1);
+            mbar_init(gempty_bar(b), 4);     // one arrival per fold warp
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tensormap(&tmap_x);
+        prefetch_tensormap(&tmap_w);
+    }
+    if (warp == 2) {
+        tmem_alloc<1>(smem_u32(tmem_slot), T::TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the fix-up kernel may be scheduled
+
+    // stream-K over (tile, group) units: the schedule of bf16_gemm.cuh with one unit = one group
+    GemmParams sp;
+    sp.num_m_blocks = 1;
+    sp.num_n_blocks = p.num_n_tiles;
+    sp.num_k_blocks = p.num_groups;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            WorkSched<0> sched(cta, num_ctas, sp);
+            WorkItem w;
+            bool ok = true;
+            while (ok && sched.next(w)) {
+                const int n0 = w.tile * T::TILE_N;
+                for (int kb = 0; kb < w.kb_count * T::GROUP_KB; kb++) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, stage)) { ok = false; break; }
+                    const int k0 = (w.kb_begin * T::GROUP_KB + kb) * T::BK;
+                    mbar_arrive_expect_tx(landed_bar(stage), T::PACKED_BYTES + T::X_BYTES);
+                    tma_load_2d(pk_base + stage * T::PACKED_BYTES, &tmap_w, landed_bar(stage), k0 / 2, n0);
+                    tma_load_2d(x_base + stage * T::X_STRIDE, &tmap_x, landed_bar(stage), k0, 0);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t instr = make_idesc(UMMA_BF16, UMMA_BF16, 128, MPAD);
+            int stage = 0;
+            uint32_t phase = 0;
+            int giter = 0;           // groups issued so far: buffer giter & 1
+            WorkSched<0> sched(cta, num_ctas, sp);
+            WorkItem w;
+            bool ok = true;
+            while (ok && sched.next(w)) {
+                for (int g = 0; g < w.kb_count && ok; g++, giter++) {
+                    const int b = giter & 1;
+                    if (!mbar_wait(gempty_bar(b), ((giter >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, b)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(b * MPAD);
+                    for (int kb = 0; kb < T::GROUP_KB; kb++) {
+                        if (!mbar_wait(ready_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        const uint64_t a_desc = make_smem_desc_k128(a_base + stage * T::A_BYTES);
+                        const uint64_t b_desc = make_smem_desc_k128(x_base + stage * T::X_STRIDE);
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            umma_f16<1>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_commit(empty_bar(stage));
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                    if (ok) umma_commit(gfull_bar(b));
+                }
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ------------------------------------------------------------------ dequantisers
+        const int r = (warp - 4) * 32 + lane;         // row of the tile this thread converts
+        int stage = 0;
+        uint32_t phase = 0;
+        WorkSched<0> sched(cta, num_ctas, sp);
+        WorkItem w;
+        bool ok = true;
+        while (ok && sched.next(w)) {
+            for (int kb = 0; kb < w.kb_count * T::GROUP_KB; kb++) {
+                // the bf16 tile of this stage is free once the stage's previous MMAs are done, which the
+                // producer has already waited for before it refilled landed[stage]
+                if (!mbar_wait(landed_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_DEQUANT, stage)) { ok = false; break; }
+                const uint4 *src = reinterpret_cast<const uint4 *>(pk_ptr + stage * T::PACKED_BYTES + r * 32);
+                const uint4 lo = src[0], hi = src[1];             // 64 weights of row r
+                const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                const uint32_t dst_row = a_base + stage * T::A_BYTES + r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; c++) {                      // 16-byte chunk c = k 8c .. 8c+7
+                    uint32_t o[4];
+                    int4x8_to_bf16x8(words[c], o);
+                    st_shared_v4(dst_row + (uint32_t)((c ^ (r & 7)) << 4), o[0], o[1], o[2], o[3]);
+                }
+                fence_proxy_async_smem();                         // make the writes visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ready_bar(stage));
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp >= 8) {
+        // ------------------------------------------------------------------ fold + epilogue
+        const int q = warp - 8;                        // == warp % 4: the TMEM lane quarter of this warp
+        const int r = q * 32 + lane;                   // weight row inside the tile = TMEM lane
+        int giter = 0;
+        WorkSched<0> sched(cta, num_ctas, sp);
+        WorkItem w;
+        bool ok = true;
+        while (ok && sched.next(w)) {
+            const int n = w.tile * T::TILE_N + r;
+            const bf16 *srow = p.scales + (size_t)(n < p.N ? n : 0) * p.num_groups + w.kb_begin;
+            float total[MPAD];
+#pragma unroll
+            for (int m = 0; m < MPAD; m++) total[m] = 0.f;
+            for (int g = 0; g < w.kb_count; g++, giter++) {
+                const int b = giter & 1;
+                const float s = __bfloat162float(srow[g]);
+                if (!mbar_wait(gfull_bar(b), (giter >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, b)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * MPAD);
+#pragma unroll
+                for (int c0 = 0; c0 < MPAD; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(t_row + (uint32_t)c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; i++) total[c0 + i] = fmaf(s, __uint_as_float(v[i]), total[c0 + i]);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(gempty_bar(b));
+            }
+            if (!ok) break;
+            if (w.part < 0) {
+                if (n < p.N) {
+#pragma unroll
+                    for (int m = 0; m < MPAD; m++)
+                        if (m < p.M) p.Y[(size_t)m * p.N + n] = __float2bfloat16_rn(total[m]);
+                }
+            } else {
+                float *slot = p.workspace + (size_t)(2 * cta + w.part) * 128 * 128 + r;
+#pragma unroll
+                for (int m = 0; m < MPAD; m++) slot[m * 128] = total[m];
+            }
+        }
+    }
+
+    __syncwarp();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, T::TMEM_COLS);
+    }
+}
+
+template <class T>
+struct W4A16Launcher {
+    static bool can_run(int M, int N, int K)
+    {
+        return M >= 1 && M <= T::MPAD && N >= 8 && N % 8 == 0 && K >= 128 && K % 128 == 0;
+    }
+    static size_t workspace_bytes(int, int, int) { return (size_t)2 * STREAMK_MAX_CTAS * 128 * 128 * sizeof(float); }
+
+    static int run(int M, int N, int K, const void *X, const void *Wq, void *Y, const void *scales, int group_size, float *workspace,
+                   size_t workspace_bytes_given, int sm_limit, cudaStream_t stream)
+    {
+        if (!can_run(M, N, K)) return set_error(GEMM_ERR_SHAPE, "shape %dx%dx%d not supported (M <= %d, K a multiple of 128)", M, N, K, T::MPAD);
+        if (group_size != 128) return set_error(GEMM_ERR_ARG, "W4A16 scale groups are 128 K-elements, got %d", group_size);
+        if (!X || !Wq || !Y || !scales) return set_error(GEMM_ERR_ARG, "null operand or scale pointer");
+        if (!workspace) return set_error(GEMM_ERR_WORKSPACE, "this configuration needs a workspace");
+        if (workspace_bytes_given != 0 && workspace_bytes_given < workspace_bytes(M, N, K))
+            return set_error(GEMM_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes_given, workspace_bytes(M, N, K));
+        DeviceInfo *dev = nullptr;
+        int rc = device_info(&dev);
+        if (rc != GEMM_OK) return rc;
+        static bool attr_set[MAX_DEVICES] = {false};
+        int devid = 0;
+        SM100_CUDA_TRY(cudaGetDevice(&devid));
+        if (!attr_set[devid]) {
+            SM100_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_ALLOC));
+            attr_set[devid] = true;
+        }
+        CUtensorMap tx, tw;
+        rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, X, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, T::MPAD, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != GEMM_OK) return rc;
+        rc = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, Wq, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, 32, T::TILE_N, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc != GEMM_OK) return rc;
+        W4A16Params p;
+        p.M = M; p.N = N; p.K = K;
+        p.num_n_tiles = (N + T::TILE_N - 1) / T::TILE_N;
+        p.num_groups = K / 128;
+        p.Y = static_cast<bf16 *>(Y);
+        p.workspace = workspace;
+        p.scales = static_cast<const bf16 *>(scales);
+        p.status = dev->status;
+        long long units = (long long)p.num_n_tiles * p.num_groups;
+        int grid = dev->sm_count;
+        if (sm_limit > 0 && sm_limit < grid) grid = sm_limit;
+        if (grid > STREAMK_MAX_CTAS) grid = STREAMK_MAX_CTAS;
+        if (grid > units) grid = (int)units;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(T::THREADS);
+        cfg.dynamicSmemBytes = T::SMEM_ALLOC;
+        cfg.stream = stream;
+        SM100_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel<T>, tx, tw, p));
+        int parts = 1;
+        while (parts < 32 && p.num_n_tiles * parts < 2 * dev->sm_count) parts *= 2;
+        cudaLaunchConfig_t rcfg = dependent_launch_config(p.num_n_tiles * parts, 256, stream);
+        SM100_CUDA_TRY(cudaLaunchKernelEx(&rcfg, streamk_reduce_kernel<128, 128>, (const float *)workspace, static_cast<bf16 *>(Y), M, N, 1,
+                                          p.num_n_tiles, 1, p.num_groups, grid, parts, 1.0f));
+        return GEMM_OK;
+    }
+};
+
+}  // namespace sm100

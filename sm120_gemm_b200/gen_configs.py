@@ -61,7 +61,10 @@ class GemmConfig:
         return GemmConfig(g[0], *(int(v) for v in g[1:]))
 
     def smem_bytes(self) -> int:
-        """Dynamic shared memory of the dense kernel; must equal UmmaGemmTraits::SMEM_ALLOC."""
+        """Dynamic shared memory of the kernel; must equal the traits' SMEM_ALLOC."""
+        if self.dt == "w4a16":   # W4A16Traits: bf16 tile + activation tile (1 KB granules) + packed int4 tile per stage
+            x = -(-self.bn * 128 // 1024) * 1024
+            return self.num_stages * (128 * 128 + x + 128 * 32) + (3 * self.num_stages + 4) * 8 + 16 + 1024
         a = 128 * 128
         b = (self.bn // self.cg) * 128
         # block-scaled kinds stage one 512-byte scale atom per 128 rows and 128 K-elements
@@ -77,6 +80,8 @@ class GemmConfig:
         """The plugin's own gemm_can_run, restated (reference: src/gemm_config.h:34-38)."""
         if M <= 0 or N <= 0 or K <= 0:
             return False
+        if self.dt == "w4a16":   # decode kernel: M fits the padded UMMA N, whole 128-element scale groups
+            return M <= self.bn and N % 8 == 0 and K % 128 == 0
         if (K * ELEM_BITS[self.dt]) % 128 != 0 or N % 8 != 0:
             return False
         if self.dt in ("mxfp8", "w4a4") and K % self.bk != 0:
@@ -112,9 +117,24 @@ def generate_block_scaled(dt: str, max_smem: int) -> list[GemmConfig]:
     return out
 
 
-def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8", "mxfp8", "w4a4")) -> list[GemmConfig]:
+def generate_w4a16(max_smem: int) -> list[GemmConfig]:
+    """W4A16 decode kernel: operands swapped (ab=1), bn = M padded to 16/32/64/128, stream-K work split."""
+    out = []
+    for mpad in (16, 32, 64, 128):
+        s = 12
+        while GemmConfig("w4a16", 128, mpad, 64, s, 1, 0, 1, 0).smem_bytes() > max_smem:
+            s -= 1
+        for st in sorted({min(s, 8), min(s, 5)}, reverse=True):
+            out.append(GemmConfig("w4a16", 128, mpad, 64, st, 1, 0, 1, 0))
+    return out
+
+
+def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8", "mxfp8", "w4a4", "w4a16")) -> list[GemmConfig]:
     out: list[GemmConfig] = []
     for dt in dts:
+        if dt == "w4a16":
+            out += generate_w4a16(max_smem)
+            continue
         if dt in ("mxfp8", "w4a4"):
             out += generate_block_scaled(dt, max_smem)
             continue
@@ -150,7 +170,7 @@ def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8", "mxfp8", "w4a
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--max-smem-kb", type=int, default=MAX_SMEM // 1024)
-    ap.add_argument("--dt", default="bf16,fp8,mxfp8,w4a4")
+    ap.add_argument("--dt", default="bf16,fp8,mxfp8,w4a4,w4a16")
     args = ap.parse_args()
     for c in generate_configs(args.max_smem_kb * 1024, tuple(args.dt.split(","))):
         print(c.name())

@@ -140,3 +140,34 @@ def test_w4a4_mxfp4(registry, cuda_device, shape):
         assert r["ok"], (k.config.name(), r)
         ran += 1
     assert ran >= 5
+
+
+def w4a16_case(M, N, K, seed):
+    """BASELINE config 5(a): X ~ N(0,1) bf16; q uniform int in [-8,7]; bf16 scale = U[0.5,2]/8 per 128 K-elements."""
+    rng = np.random.default_rng(seed)
+    X = o.f32_to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    q = rng.integers(-8, 8, (N, K)).astype(np.int8)
+    sc = o.f32_to_bf16_bits((rng.uniform(0.5, 2.0, (N, K // 128)) / 8).astype(np.float32))
+    return X, q, sc
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 128), (16, 256, 256), (16, 1024, 1024), (128, 512, 2048), (7, 136, 384), (100, 4096, 1024),
+                                   (1, 28672, 8192), (16, 28672, 8192), (128, 28672, 8192)])
+def test_w4a16(registry, cuda_device, shape):
+    M, N, K = shape
+    X, q, sc = w4a16_case(M, N, K, seed=4)
+    packed = o.int4_pack(q)
+    ref = o.gemm_f32(o.bf16_bits_to_f32(X), o.int4_dequantise(packed, sc, 128))
+    Xd = torch.from_numpy(X.view(np.int16)).cuda().view(torch.bfloat16)
+    Wd = torch.from_numpy(packed).cuda()
+    Sd = torch.from_numpy(sc.view(np.int16)).cuda().view(torch.bfloat16)
+    ran = 0
+    for k in registry.kernels:
+        if k.config.dt != "w4a16" or not k.can_run(M, N, K):
+            continue
+        Y = to_bits(run_ex(k, M, N, K, Xd, Wd, w_scale=Sd, group_size=128))
+        assert not np.isnan(o.bf16_bits_to_f32(Y)).any(), k.config.name()
+        r = o.check_quantised(Y, ref)
+        assert r["ok"], (k.config.name(), shape, r)
+        ran += 1
+    assert ran >= 2

@@ -65,6 +65,8 @@ def test_validity_rules_match_plugins(registry):
             assert bool(k.can_run(M, N, K)) == k.config.is_valid_for(M, N, K), (k.config.name(), M, N, K)
         if k.config.split_k > 1:
             assert k.workspace_bytes(128, 4096, 14336) == k.config.split_k * 128 * 4096 * 4
+        elif k.config.dt == "w4a16":
+            assert k.workspace_bytes(16, 4096, 14336) == 2 * 160 * 128 * 128 * 4
         elif k.config.split_k == 0:   # stream-K: two partial-tile slots per CTA (pair), shape-independent
             assert k.workspace_bytes(128, 4096, 14336) == 2 * (160 // k.config.cg) * k.config.bm * k.config.bn * 4
         else:
