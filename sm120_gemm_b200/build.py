@@ -74,10 +74,28 @@ def build_util(force: bool = False) -> str:
     return UTIL_LIB
 
 
+BENCH_BIN = os.path.join(KERNEL_DIR, "bench")
+
+
+def build_bench(force: bool = False) -> str:
+    """The C++ harness (csrc/bench.cu): autotune / quick / debug modes, cuBLAS beside."""
+    src = os.path.join(CSRC, "bench.cu")
+    if not force and os.path.exists(BENCH_BIN) and os.path.getmtime(BENCH_BIN) >= _deps_mtime():
+        return BENCH_BIN
+    os.makedirs(KERNEL_DIR, exist_ok=True)
+    cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-ccbin", "/usr/bin/g++",
+           "-diag-suppress", "177", f'-DKERNEL_DIR="{KERNEL_DIR}"', "-o", BENCH_BIN, src, "-lcublas", "-ldl"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for bench.cu:\n{r.stdout}\n{r.stderr}")
+    return BENCH_BIN
+
+
 def build_all(configs=None, force: bool = False, jobs: int | None = None) -> list[str]:
     configs = list(configs) if configs is not None else generate_configs()
     jobs = jobs or max(1, (os.cpu_count() or 2))
     build_util(force)
+    build_bench(force)
     with ThreadPoolExecutor(jobs) as ex:
         return list(ex.map(lambda c: build_one(c, force), configs))
 

@@ -11,11 +11,18 @@
 // (Folding the scale into a bf16 weight instead, bf16(q*s), rounds every weight and misses
 // the 1e-3 accuracy bar.)
 //
-// Warps (384 threads):  0 TMA producer | 1 MMA issuer | 2 TMEM alloc | 3 idle
-//                       4-7  dequantisers: thread r converts row r of the tile (64 weights per k-block)
-//                       8-11 fold + epilogue: thread r owns weight row r (TMEM lane r)
-// Barriers per ring stage: landed[s] (TMA bytes: packed weights + activations) -> dequantisers;
-//   ready[s] (bf16 tile written) -> MMA; empty[s] (tcgen05.commit) -> producer.
+// Warps:  0 TMA producer | 1 MMA issuer | 2 TMEM alloc | 3 idle
+//         4-7  fold + epilogue: thread r owns weight row r (TMEM lane r)
+//         8..  dequantiser teams of 4 warps: thread r of a team converts row r of the tile (64 weights
+//              per k-block); teams take k-blocks in turn so conversion latency overlaps
+// Two rings.  The LOAD ring has stages of 256 K-elements: one TMA box of 128 rows x 128 bytes of
+// packed int4 (whole 128-byte runs per weight row: 32-byte runs waste most of a DRAM burst) plus
+// the four 64-element activation boxes of the same K range.  The TILE ring holds the dequantised
+// bf16 tiles, one per 64-element k-block.
+//   landed[p]  TMA bytes of load stage p            -> dequantisers (and, through them, the MMA issuer)
+//   lfree[p]   tcgen05.commit after the stage's last MMA -> producer
+//   ready[s]   bf16 tile s written                  -> MMA issuer
+//   tfree[s]   tcgen05.commit of the MMAs on tile s -> dequantisers
 // Per group buffer b (2): gfull[b] (commit after the group's 2nd k-block) -> fold; gempty[b] -> MMA.
 //
 // Work is cut stream-K fashion in units of one group: every CTA gets the same number of
@@ -39,21 +46,27 @@ struct W4A16Params {
 template <int MPAD_, int STAGES_>
 struct W4A16Traits {
     static constexpr int MPAD = MPAD_;                 // UMMA N: M rounded up (16, 32, 64 or 128)
-    static constexpr int STAGES = STAGES_;
+    static constexpr int STAGES = STAGES_;             // bf16 tile ring
     static constexpr int TILE_N = 128;                 // weight rows per tile = TMEM lanes
-    static constexpr int BK = 64;                      // K elements per ring stage (128 bytes of bf16)
+    static constexpr int BK = 64;                      // K elements per bf16 tile (128 bytes)
     static constexpr int GROUP_KB = 2;                 // k-blocks per scale group (128 / 64)
-    static constexpr int PACKED_BYTES = TILE_N * BK / 2;   // 4 KB of int4
-    static constexpr int X_BYTES = MPAD_ * 128;
-    static constexpr int A_BYTES = TILE_N * 128;       // dequantised bf16 tile
-    static constexpr int STAGE_SMEM = A_BYTES + ((X_BYTES + 1023) / 1024 * 1024) + PACKED_BYTES;
+    static constexpr int LOAD_KB = 4;                  // k-blocks per load stage (256 K-elements = 128 packed bytes per row)
+    static constexpr int PACKED_BYTES = TILE_N * 128;  // 16 KB of int4 per load stage
+    static constexpr int X_BYTES = MPAD_ * 128;        // one activation box
     static constexpr int X_STRIDE = (X_BYTES + 1023) / 1024 * 1024;
-    static constexpr int NUM_BARRIERS = 3 * STAGES_ + 4;
-    static constexpr int SMEM_BYTES = STAGES_ * STAGE_SMEM + NUM_BARRIERS * 8 + 16;
+    static constexpr int LOAD_STAGE_SMEM = PACKED_BYTES + LOAD_KB * X_STRIDE;
+    static constexpr int LOAD_TX_BYTES = PACKED_BYTES + LOAD_KB * X_BYTES;
+    static constexpr int A_BYTES = TILE_N * 128;       // dequantised bf16 tile
+    static constexpr int LOAD_STAGES_FIT = (224 * 1024 - STAGES_ * A_BYTES) / LOAD_STAGE_SMEM;
+    static constexpr int LOAD_STAGES = LOAD_STAGES_FIT > 4 ? 4 : LOAD_STAGES_FIT;
+    static constexpr int NUM_BARRIERS = 2 * STAGES_ + 2 * LOAD_STAGES + 4;
+    static constexpr int SMEM_BYTES = STAGES_ * A_BYTES + LOAD_STAGES * LOAD_STAGE_SMEM + NUM_BARRIERS * 8 + 16;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
     static constexpr int TMEM_COLS = 2 * MPAD_ <= 32 ? 32 : 2 * MPAD_ <= 64 ? 64 : 2 * MPAD_ <= 128 ? 128 : 256;
-    static constexpr int THREADS = 384;
+    static constexpr int TEAMS = MPAD_ <= 64 ? 2 : 1;   // dequantiser teams (the M = 128 fold needs the registers)
+    static constexpr int THREADS = 256 + 128 * TEAMS;
     static_assert(MPAD_ == 16 || MPAD_ == 32 || MPAD_ == 64 || MPAD_ == 128, "padded M is 16, 32, 64 or 128");
+    static_assert(LOAD_STAGES >= 2, "at least two load stages must fit");
     static_assert(SMEM_ALLOC <= 232448, "exceeds the shared memory of one CTA");
 };
 
@@ -77,7 +90,7 @@ __device__ __forceinline__ void int4x8_to_bf16x8(uint32_t w, uint32_t (&out)[4])
 }
 
 template <class T>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(T::THREADS, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const W4A16Params p)
 {
     constexpr int STAGES = T::STAGES;
@@ -86,28 +99,32 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_base - raw_addr);
-    const uint32_t a_base = smem_base;                                   // bf16 weight tiles
-    const uint32_t x_base = a_base + STAGES * T::A_BYTES;                // activation tiles
-    const uint32_t pk_base = x_base + STAGES * T::X_STRIDE;              // packed int4 tiles
-    const uint32_t bar_base = pk_base + STAGES * T::PACKED_BYTES;
+    constexpr int LSTAGES = T::LOAD_STAGES;
+    const uint32_t a_base = smem_base;                                   // bf16 weight tiles (tile ring)
+    const uint32_t ld_base = a_base + STAGES * T::A_BYTES;               // load ring: [packed 16 KB][4 activation boxes]
+    const uint32_t bar_base = ld_base + LSTAGES * T::LOAD_STAGE_SMEM;
     auto landed_bar = [&](int s) { return bar_base + 8u * s; };
-    auto ready_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
-    auto gfull_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + b); };
-    auto gempty_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 + b); };
+    auto lfree_bar = [&](int s) { return bar_base + 8u * (LSTAGES + s); };
+    auto ready_bar = [&](int s) { return bar_base + 8u * (2 * LSTAGES + s); };
+    auto tfree_bar = [&](int s) { return bar_base + 8u * (2 * LSTAGES + STAGES + s); };
+    auto gfull_bar = [&](int b) { return bar_base + 8u * (2 * LSTAGES + 2 * STAGES + b); };
+    auto gempty_bar = [&](int b) { return bar_base + 8u * (2 * LSTAGES + 2 * STAGES + 2 + b); };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (bar_base - smem_base) + 8u * T::NUM_BARRIERS);
     volatile uint32_t *abort_flag = tmem_slot + 1;
-    const uint8_t *pk_ptr = smem + (pk_base - smem_base);
+    const uint8_t *ld_ptr = smem + (ld_base - smem_base);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int cta = blockIdx.x, num_ctas = gridDim.x;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
+        for (int s = 0; s < LSTAGES; s++) {
             mbar_init(landed_bar(s), 1);
-            mbar_init(ready_bar(s), 4);      // one arrival per dequantiser warp
-            mbar_init(empty_bar(s), 1);
+            mbar_init(lfree_bar(s), 1);
+        }
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(ready_bar(s), 4);      // one arrival per warp of the dequantiser team that wrote the tile
+            mbar_init(tfree_bar(s), 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(gfull_bar(b), 1);
@@ -136,86 +153,116 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     sp.num_k_blocks = p.num_groups;
 
     if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int pcount = 0;                            // load stages issued so far
             WorkSched<0> sched(cta, num_ctas, sp);
             WorkItem w;
             bool ok = true;
             while (ok && sched.next(w)) {
                 const int n0 = w.tile * T::TILE_N;
-                for (int kb = 0; kb < w.kb_count * T::GROUP_KB; kb++) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, stage)) { ok = false; break; }
+                const int item_kb = w.kb_count * T::GROUP_KB;
+                for (int kb = 0; kb < item_kb; kb += T::LOAD_KB, pcount++) {
+                    const int ps = pcount % LSTAGES;
+                    if (!mbar_wait(lfree_bar(ps), (((uint32_t)(pcount / LSTAGES)) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, ps)) {
+                        ok = false;
+                        break;
+                    }
                     const int k0 = (w.kb_begin * T::GROUP_KB + kb) * T::BK;
-                    mbar_arrive_expect_tx(landed_bar(stage), T::PACKED_BYTES + T::X_BYTES);
-                    tma_load_2d(pk_base + stage * T::PACKED_BYTES, &tmap_w, landed_bar(stage), k0 / 2, n0);
-                    tma_load_2d(x_base + stage * T::X_STRIDE, &tmap_x, landed_bar(stage), k0, 0);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    const uint32_t dst = ld_base + ps * T::LOAD_STAGE_SMEM;
+                    // always the full 256-element box: past an item's end it brings unused (or zero-filled) data
+                    mbar_arrive_expect_tx(landed_bar(ps), T::LOAD_TX_BYTES);
+                    tma_load_2d(dst, &tmap_w, landed_bar(ps), k0 / 2, n0);
+#pragma unroll
+                    for (int j = 0; j < T::LOAD_KB; j++)
+                        tma_load_2d(dst + T::PACKED_BYTES + j * T::X_STRIDE, &tmap_x, landed_bar(ps), k0 + j * T::BK, 0);
                 }
             }
         }
     } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t instr = make_idesc(UMMA_BF16, UMMA_BF16, 128, MPAD);
-            int stage = 0;
-            uint32_t phase = 0;
+            int kcount = 0;          // k-blocks issued so far: tile ring slot kcount % STAGES
+            int pcount = 0;          // load stages consumed so far
             int giter = 0;           // groups issued so far: buffer giter & 1
             WorkSched<0> sched(cta, num_ctas, sp);
             WorkItem w;
             bool ok = true;
             while (ok && sched.next(w)) {
-                for (int g = 0; g < w.kb_count && ok; g++, giter++) {
+                const int item_kb = w.kb_count * T::GROUP_KB;
+                for (int kb = 0; kb < item_kb && ok; kb++, kcount++) {
+                    const int j = kb % T::LOAD_KB;                 // k-block inside its load stage
+                    const int ps = pcount % LSTAGES;
                     const int b = giter & 1;
-                    if (!mbar_wait(gempty_bar(b), ((giter >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, b)) { ok = false; break; }
+                    if (kb % T::GROUP_KB == 0) {
+                        if (!mbar_wait(gempty_bar(b), ((giter >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, b)) { ok = false; break; }
+                        tc_fence_after_sync();
+                    }
+                    const int st = kcount % STAGES;
+                    // ready[st] also tells that the load stage has landed: the dequantisers waited for it
+                    if (!mbar_wait(ready_bar(st), ((uint32_t)(kcount / STAGES)) & 1u, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, st)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + (uint32_t)(b * MPAD);
-                    for (int kb = 0; kb < T::GROUP_KB; kb++) {
-                        if (!mbar_wait(ready_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage)) { ok = false; break; }
-                        tc_fence_after_sync();
-                        const uint64_t a_desc = make_smem_desc_k128(a_base + stage * T::A_BYTES);
-                        const uint64_t b_desc = make_smem_desc_k128(x_base + stage * T::X_STRIDE);
+                    const uint64_t a_desc = make_smem_desc_k128(a_base + st * T::A_BYTES);
+                    const uint64_t b_desc = make_smem_desc_k128(ld_base + ps * T::LOAD_STAGE_SMEM + T::PACKED_BYTES + j * T::X_STRIDE);
+#ifndef W4_SKIP_MMA
 #pragma unroll
-                        for (int k = 0; k < 4; k++)
-                            umma_f16<1>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, (kb > 0 || k > 0) ? 1u : 0u);
-                        umma_commit(empty_bar(stage));
-                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                    }
-                    if (ok) umma_commit(gfull_bar(b));
+                    for (int k = 0; k < 4; k++)
+                        umma_f16<1>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, (kb % T::GROUP_KB > 0 || k > 0) ? 1u : 0u);
+#endif
+                    umma_commit(tfree_bar(st));
+                    if (kb % T::GROUP_KB == T::GROUP_KB - 1) { umma_commit(gfull_bar(b)); giter++; }
+                    if (j == T::LOAD_KB - 1 || kb == item_kb - 1) { umma_commit(lfree_bar(ps)); pcount++; }
                 }
             }
         }
-    } else if (warp >= 4 && warp < 8) {
+    } else if (warp >= 8) {
         // ------------------------------------------------------------------ dequantisers
-        const int r = (warp - 4) * 32 + lane;         // row of the tile this thread converts
-        int stage = 0;
-        uint32_t phase = 0;
+        const int team = (warp - 8) >> 2;
+        const int r = ((warp - 8) & 3) * 32 + lane;   // row of the tile this thread converts
+        int kcount = 0;                                // k-blocks seen so far (all teams count alike)
+        int pcount = 0;
         WorkSched<0> sched(cta, num_ctas, sp);
         WorkItem w;
         bool ok = true;
         while (ok && sched.next(w)) {
-            for (int kb = 0; kb < w.kb_count * T::GROUP_KB; kb++) {
-                // the bf16 tile of this stage is free once the stage's previous MMAs are done, which the
-                // producer has already waited for before it refilled landed[stage]
-                if (!mbar_wait(landed_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_DEQUANT, stage)) { ok = false; break; }
-                const uint4 *src = reinterpret_cast<const uint4 *>(pk_ptr + stage * T::PACKED_BYTES + r * 32);
-                const uint4 lo = src[0], hi = src[1];             // 64 weights of row r
+            const int item_kb = w.kb_count * T::GROUP_KB;
+            for (int kb = 0; kb < item_kb; kb++, kcount++) {
+                const int j = kb % T::LOAD_KB;
+                const int ps = pcount % LSTAGES;
+                const uint32_t pphase = ((uint32_t)(pcount / LSTAGES)) & 1u;
+                if (j == T::LOAD_KB - 1 || kb == item_kb - 1) pcount++;
+                if (kcount % T::TEAMS != team) continue;
+                const int st = kcount % STAGES;
+                if (!mbar_wait(landed_bar(ps), pphase, abort_flag, p.status, ST_TIMEOUT_DEQUANT, ps)) { ok = false; break; }
+                if (!mbar_wait(tfree_bar(st), (((uint32_t)(kcount / STAGES)) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_DEQUANT, 16 + st)) { ok = false; break; }
+                // packed row r: 128 bytes, 128B-swizzled by the TMA; k-block j is its 16-byte chunks 2j and 2j+1
+                const uint8_t *row = ld_ptr + ps * T::LOAD_STAGE_SMEM + r * 128;
+                const uint4 lo = *reinterpret_cast<const uint4 *>(row + (((2 * j) ^ (r & 7)) << 4));
+                const uint4 hi = *reinterpret_cast<const uint4 *>(row + (((2 * j + 1) ^ (r & 7)) << 4));
                 const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                const uint32_t dst_row = a_base + stage * T::A_BYTES + r * 128;
+                const uint32_t dst_row = a_base + st * T::A_BYTES + r * 128;
+#ifndef W4_SKIP_DEQUANT
 #pragma unroll
                 for (int c = 0; c < 8; c++) {                      // 16-byte chunk c = k 8c .. 8c+7
                     uint32_t o[4];
                     int4x8_to_bf16x8(words[c], o);
                     st_shared_v4(dst_row + (uint32_t)((c ^ (r & 7)) << 4), o[0], o[1], o[2], o[3]);
                 }
+#else
+                if (words[0] == 0x12345678u) st_shared_v4(dst_row, words[1], words[2], words[3], words[4]);
+#endif
+#ifndef W4_SKIP_FENCE
                 fence_proxy_async_smem();                         // make the writes visible to the tensor core's reads
+#endif
                 __syncwarp();
-                if (lane == 0) mbar_arrive(ready_bar(stage));
-                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                if (lane == 0) mbar_arrive(ready_bar(st));
             }
         }
-    } else if (warp >= 8) {
+    } else if (warp >= 4) {
         // ------------------------------------------------------------------ fold + epilogue
-        const int q = warp - 8;                        // == warp % 4: the TMEM lane quarter of this warp
+        const int q = warp - 4;                        // == warp % 4: the TMEM lane quarter of this warp
         const int r = q * 32 + lane;                   // weight row inside the tile = TMEM lane
         int giter = 0;
         WorkSched<0> sched(cta, num_ctas, sp);
@@ -227,23 +274,41 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             float total[MPAD];
 #pragma unroll
             for (int m = 0; m < MPAD; m++) total[m] = 0.f;
-            for (int g = 0; g < w.kb_count; g++, giter++) {
-                const int b = giter & 1;
-                const float s = __bfloat162float(srow[g]);
-                if (!mbar_wait(gfull_bar(b), (giter >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, b)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * MPAD);
+            // scales are fetched eight groups ahead of their use: a load issued where it is needed would put
+            // an L2 round trip into every group and throttle the whole pipeline
+            float s_cur[8], s_nxt[8];
 #pragma unroll
-                for (int c0 = 0; c0 < MPAD; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld_32x16(t_row + (uint32_t)c0, v);
-                    tmem_ld_wait();
+            for (int i = 0; i < 8; i++) s_cur[i] = i < w.kb_count ? __bfloat162float(srow[i]) : 0.f;
+            for (int g0 = 0; g0 < w.kb_count && ok; g0 += 8) {
 #pragma unroll
-                    for (int i = 0; i < 16; i++) total[c0 + i] = fmaf(s, __uint_as_float(v[i]), total[c0 + i]);
+                for (int i = 0; i < 8; i++) s_nxt[i] = g0 + 8 + i < w.kb_count ? __bfloat162float(srow[g0 + 8 + i]) : 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    if (g0 + i >= w.kb_count) break;
+                    const int b = giter & 1;
+                    const float s = s_cur[i];
+                    if (!mbar_wait(gfull_bar(b), (giter >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, b)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * MPAD);
+#ifndef W4_SKIP_FOLD
+#pragma unroll
+                    for (int c0 = 0; c0 < MPAD; c0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld_32x16(t_row + (uint32_t)c0, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 16; e++) total[c0 + e] = fmaf(s, __uint_as_float(v[e]), total[c0 + e]);
+                    }
+#else
+                    total[0] += s; (void)t_row;
+#endif
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(gempty_bar(b));
+                    giter++;
                 }
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(gempty_bar(b));
+#pragma unroll
+                for (int i = 0; i < 8; i++) s_cur[i] = s_nxt[i];
             }
             if (!ok) break;
             if (w.part < 0) {
@@ -302,7 +367,7 @@ struct W4A16Launcher {
         CUtensorMap tx, tw;
         rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, X, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, T::MPAD, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != GEMM_OK) return rc;
-        rc = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, Wq, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, 32, T::TILE_N, CU_TENSOR_MAP_SWIZZLE_NONE);
+        rc = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, Wq, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, 128, T::TILE_N, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != GEMM_OK) return rc;
         W4A16Params p;
         p.M = M; p.N = N; p.K = K;

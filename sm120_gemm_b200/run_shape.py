@@ -14,6 +14,71 @@ import os
 import sys
 
 
+def time_lowp_kernel(kern, M, N, K, warmup=5, repeat=20, spacer_us=100, rotate=True, seed=0):
+    """Same protocol for the fp8 / mxfp8 / w4a4 / w4a16 plugins (gemm_run_ex), random operand bits."""
+    import torch
+
+    import sm120_gemm_b200 as g
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    util = g.util_lib()
+    dt = kern.config.dt
+    gen = torch.Generator(device=dev); gen.manual_seed(seed)
+    wbits = {"fp8": 8, "mxfp8": 8, "w4a4": 4, "w4a16": 4}[dt]
+    xbits = 16 if dt == "w4a16" else wbits
+    l2 = torch.cuda.get_device_properties(dev).L2_cache_size
+    per_set = M * K * xbits // 8 + N * K * wbits // 8 + M * N * 2
+    nbuf = min(64, max(1, -(-2 * l2 // per_set))) if rotate else 1
+
+    def rand_bytes(rows, nbytes):
+        # bytes below 0x78 in both nibbles: finite e4m3 / e2m1 codes of either sign are all fine as data
+        return torch.randint(0, 0x77, (rows, nbytes), dtype=torch.uint8, device=dev, generator=gen)
+
+    sets = []
+    for _ in range(nbuf):
+        W = rand_bytes(N, K * wbits // 8)
+        X = torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16) if dt == "w4a16" else rand_bytes(M, K * xbits // 8)
+        sets.append((X, W, torch.empty((M, N), dtype=torch.bfloat16, device=dev)))
+    a = g.GemmArgs()
+    a.M, a.N, a.K, a.group_size = M, N, K, 128
+    a.x_scale_f = a.w_scale_f = 1.0 / 16
+    keep = []
+    if dt in ("mxfp8", "w4a4"):
+        sx = torch.full((util.gemm_mx_tiled_scale_bytes(M, K),), 124, dtype=torch.uint8, device=dev)
+        sw = torch.full((util.gemm_mx_tiled_scale_bytes(N, K),), 124, dtype=torch.uint8, device=dev)
+        a.x_scale, a.w_scale = sx.data_ptr(), sw.data_ptr()
+        keep += [sx, sw]
+    if dt == "w4a16":
+        sw = (torch.rand((N, K // 128), device=dev, generator=gen) * 0.2 + 0.05).to(torch.bfloat16)
+        a.w_scale = sw.data_ptr()
+        keep.append(sw)
+    wsb = kern.workspace_bytes(M, N, K)
+    ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+    a.workspace, a.workspace_bytes = (ws.data_ptr() if wsb else None), wsb
+    a.stream = torch.cuda.current_stream().cuda_stream
+    idx = [0]
+
+    def launch():
+        X, W, Y = sets[idx[0] % nbuf]
+        idx[0] += 1
+        a.X, a.W, a.Y = X.data_ptr(), W.data_ptr(), Y.data_ptr()
+        g.dispatch_ex(kern, a)
+
+    for _ in range(warmup):
+        launch()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(repeat)]
+    for e0, e1 in ev:
+        e0.record()
+        launch()
+        e1.record()
+        util.gemm_spacer(spacer_us, a.stream)
+    torch.cuda.synchronize()
+    kern.check_status()
+    scale_bytes = {"fp8": 8, "mxfp8": (M + N) * K // 32, "w4a4": (M + N) * K // 32, "w4a16": N * K // 128 * 2}[dt]
+    return sum(e0.elapsed_time(e1) for e0, e1 in ev) / repeat, nbuf, per_set + scale_bytes
+
+
 def time_kernel(kern, M, N, K, warmup=5, repeat=20, spacer_us=100, rotate=True, dist="normal", seed=0):
     import torch
 
@@ -76,9 +141,12 @@ def main():
     kern = g.load_plugin(os.path.join(g.KERNEL_DIR, f"libgemm_{args.kernel}.so"))
     if not kern.can_run(M, N, K):
         sys.exit(f"{args.kernel} cannot run {M}x{N}x{K}")
-    ms, nbuf = time_kernel(kern, M, N, K, args.warmup, args.repeat, rotate=not args.no_rotate, dist=args.dist)
+    if kern.config.dt == "bf16":
+        ms, nbuf = time_kernel(kern, M, N, K, args.warmup, args.repeat, rotate=not args.no_rotate, dist=args.dist)
+        algo_bytes = (M * K + N * K + M * N) * 2
+    else:
+        ms, nbuf, algo_bytes = time_lowp_kernel(kern, M, N, K, args.warmup, args.repeat, rotate=not args.no_rotate)
     flops = 2.0 * M * N * K
-    algo_bytes = (M * K + N * K + M * N) * 2
     print(json.dumps({"kernel": args.kernel, "shape": [M, N, K], "ms": ms, "tflops": flops / ms / 1e9,
                       "algorithmic_gbs": algo_bytes / ms / 1e6, "buffer_sets": nbuf}))
 
