@@ -83,11 +83,11 @@ struct GemmConfig {
     // a plugin reports the exact figure through gemm_smem_bytes()).
     size_t smem_bytes() const
     {
-        if (dt == GEMM_DT_W4A16) {   // bf16 tile ring (num_stages) + load ring (16 KB packed + 4 activation boxes per stage)
+        if (dt == GEMM_DT_W4A16) {   // group ring (num_stages slots of two bf16 tiles) + load ring (16 KB packed + 4 activation boxes)
             const size_t load_stage = 128 * 128 + 4 * (((size_t)bn * 128 + 1023) / 1024 * 1024);
-            const size_t fit = (224 * 1024 - (size_t)num_stages * 128 * 128) / load_stage;
+            const size_t fit = (224 * 1024 - (size_t)num_stages * 2 * 128 * 128) / load_stage;
             const size_t load_stages = fit > 4 ? 4 : fit;
-            return num_stages * 128 * 128 + load_stages * load_stage + (2 * (size_t)num_stages + 2 * load_stages + 4) * 8 + 16 + 1024;
+            return (size_t)num_stages * 2 * 128 * 128 + load_stages * load_stage + (2 * load_stages + 3 * (size_t)num_stages) * 8 + 16 + 1024;
         }
         const size_t k_atoms = (dt == GEMM_DT_MXFP8 || dt == GEMM_DT_W4A4) ? bk / 128 : 0;   // 512-byte scale atoms per stage
         const size_t sf_ring = (num_stages * k_atoms * (1 + (bn + 127) / 128) * 512 + 1023) / 1024 * 1024;

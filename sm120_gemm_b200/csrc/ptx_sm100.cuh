@@ -3,7 +3,7 @@
 //
 // Same role as the PTX helper block of the reference (src/bf16_gemm.cuh:10-178), rebuilt
 // for the Blackwell data-centre ISA.  Differences that matter:
-//   * every wait is bounded: after WAIT_LIMIT_NS without progress the waiter raises a
+//   * every wait is bounded: after WAIT_LIMIT_CYCLES without progress the waiter raises a
 //     CTA-wide abort flag, records where it gave up and returns false.  The reference
 //     spins forever (src/bf16_gemm.cuh:137-148).
 //   * no TMA load carries a cluster-multicast qualifier anywhere in this file.
@@ -14,9 +14,11 @@
 
 namespace sm100 {
 
-// A wait that sees no progress for this long gives up (the longest legitimate wait is one
-// output tile's main loop, well under 10 ms even for K = 64k).
-static constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+// A wait that sees no progress for this many SM clock cycles gives up: about 2 s at the
+// 1.0-1.97 GHz the part runs at (the longest legitimate wait is one output tile's main loop,
+// well under 10 ms even for K = 64k).  The SM's own cycle counter is used because it is cheap
+// to read; %globaltimer is not.
+static constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;
 
 // Codes written to the device status word by a wait that gave up.
 enum : uint32_t {
@@ -122,7 +124,11 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
+#ifdef SM100_SPIN_TEST_WAIT
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(done)
@@ -138,13 +144,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           uint32_t *status, uint32_t code, uint32_t detail)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = globaltimer_ns();
+    long long t0 = 0;
     uint32_t spins = 0;
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0xffu) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
                 if (status != nullptr && atomicCAS(status, 0u, code) == 0u) {
                     status[1] = blockIdx.x;

@@ -11,19 +11,22 @@
 // (Folding the scale into a bf16 weight instead, bf16(q*s), rounds every weight and misses
 // the 1e-3 accuracy bar.)
 //
-// Warps:  0 TMA producer | 1 MMA issuer | 2 TMEM alloc | 3 idle
+// Warps:  0 TMA producer | 1 and 3 MMA issuers (even / odd groups) | 2 TMEM alloc
 //         4-7  fold + epilogue: thread r owns weight row r (TMEM lane r)
-//         8..  dequantiser teams of 4 warps: thread r of a team converts row r of the tile (64 weights
-//              per k-block); teams take k-blocks in turn so conversion latency overlaps
-// Two rings.  The LOAD ring has stages of 256 K-elements: one TMA box of 128 rows x 128 bytes of
-// packed int4 (whole 128-byte runs per weight row: 32-byte runs waste most of a DRAM burst) plus
-// the four 64-element activation boxes of the same K range.  The TILE ring holds the dequantised
-// bf16 tiles, one per 64-element k-block.
-//   landed[p]  TMA bytes of load stage p            -> dequantisers (and, through them, the MMA issuer)
-//   lfree[p]   tcgen05.commit after the stage's last MMA -> producer
-//   ready[s]   bf16 tile s written                  -> MMA issuer
-//   tfree[s]   tcgen05.commit of the MMAs on tile s -> dequantisers
-// Per group buffer b (2): gfull[b] (commit after the group's 2nd k-block) -> fold; gempty[b] -> MMA.
+//         8..  dequantiser teams of 4 warps: thread r of a team converts row r of the tile; with two
+//              teams each takes one of a group's two k-blocks
+// The unit of the pipeline is one scale GROUP (128 K-elements = two 64-element bf16 tiles): a single
+// thread's tcgen05 instructions cost ~60-80 cycles each to issue and these MMAs are tiny, so issuing is
+// the scarce resource: 8 MMAs and one commit per group, and two issuer threads taking groups in turn.
+// LOAD ring, stages of 256 K-elements (two groups): one TMA box of 128 rows x 128 bytes of packed
+// int4 plus the four 64-element activation boxes of the same K range.
+//   landed[p]  TMA bytes of load stage p                    -> dequantisers
+//   lfree[p]   tcgen05.commit by the issuer of each of the stage's groups (2 arrivals) -> producer
+// GROUP ring, slot = two bf16 tiles in shared memory + one accumulator buffer in TMEM:
+//   ready[s]   both tiles of the group written              -> MMA issuer
+//   gdone[s]   tcgen05.commit after the group's 8 MMAs      -> fold warps (accumulator complete) and
+//              dequantisers (tiles may be overwritten)
+//   gempty[s]  fold warps have read the accumulator         -> MMA issuer
 //
 // Work is cut stream-K fashion in units of one group: every CTA gets the same number of
 // groups; a range that does not cover a tile's whole K leaves an FP32 partial [m][128] in the
@@ -46,26 +49,30 @@ struct W4A16Params {
 template <int MPAD_, int STAGES_>
 struct W4A16Traits {
     static constexpr int MPAD = MPAD_;                 // UMMA N: M rounded up (16, 32, 64 or 128)
-    static constexpr int STAGES = STAGES_;             // bf16 tile ring
+    static constexpr int STAGES = STAGES_;             // group ring slots
     static constexpr int TILE_N = 128;                 // weight rows per tile = TMEM lanes
     static constexpr int BK = 64;                      // K elements per bf16 tile (128 bytes)
-    static constexpr int GROUP_KB = 2;                 // k-blocks per scale group (128 / 64)
-    static constexpr int LOAD_KB = 4;                  // k-blocks per load stage (256 K-elements = 128 packed bytes per row)
+    static constexpr int GROUP_KB = 2;                 // bf16 tiles per scale group (128 / 64)
+    static constexpr int LOAD_GROUPS = 2;              // groups per load stage (256 K-elements = 128 packed bytes per row)
+    static constexpr int LOAD_KB = LOAD_GROUPS * GROUP_KB;
     static constexpr int PACKED_BYTES = TILE_N * 128;  // 16 KB of int4 per load stage
     static constexpr int X_BYTES = MPAD_ * 128;        // one activation box
     static constexpr int X_STRIDE = (X_BYTES + 1023) / 1024 * 1024;
     static constexpr int LOAD_STAGE_SMEM = PACKED_BYTES + LOAD_KB * X_STRIDE;
     static constexpr int LOAD_TX_BYTES = PACKED_BYTES + LOAD_KB * X_BYTES;
-    static constexpr int A_BYTES = TILE_N * 128;       // dequantised bf16 tile
-    static constexpr int LOAD_STAGES_FIT = (224 * 1024 - STAGES_ * A_BYTES) / LOAD_STAGE_SMEM;
+    static constexpr int A_BYTES = TILE_N * 128;       // one dequantised bf16 tile
+    static constexpr int SLOT_BYTES = GROUP_KB * A_BYTES;
+    static constexpr int LOAD_STAGES_FIT = (224 * 1024 - STAGES_ * SLOT_BYTES) / LOAD_STAGE_SMEM;
     static constexpr int LOAD_STAGES = LOAD_STAGES_FIT > 4 ? 4 : LOAD_STAGES_FIT;
-    static constexpr int NUM_BARRIERS = 2 * STAGES_ + 2 * LOAD_STAGES + 4;
-    static constexpr int SMEM_BYTES = STAGES_ * A_BYTES + LOAD_STAGES * LOAD_STAGE_SMEM + NUM_BARRIERS * 8 + 16;
+    static constexpr int NUM_BARRIERS = 2 * LOAD_STAGES + 3 * STAGES_;
+    static constexpr int SMEM_BYTES = STAGES_ * SLOT_BYTES + LOAD_STAGES * LOAD_STAGE_SMEM + NUM_BARRIERS * 8 + 16;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
-    static constexpr int TMEM_COLS = 2 * MPAD_ <= 32 ? 32 : 2 * MPAD_ <= 64 ? 64 : 2 * MPAD_ <= 128 ? 128 : 256;
+    static constexpr int ACC_COLS = STAGES_ * MPAD_;   // one accumulator buffer per group slot
+    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
     static constexpr int TEAMS = MPAD_ <= 64 ? 2 : 1;   // dequantiser teams (the M = 128 fold needs the registers)
     static constexpr int THREADS = 256 + 128 * TEAMS;
     static_assert(MPAD_ == 16 || MPAD_ == 32 || MPAD_ == 64 || MPAD_ == 128, "padded M is 16, 32, 64 or 128");
+    static_assert(STAGES_ >= 2 && ACC_COLS <= 512, "2 or more group slots whose accumulators fit in TMEM");
     static_assert(LOAD_STAGES >= 2, "at least two load stages must fit");
     static_assert(SMEM_ALLOC <= 232448, "exceeds the shared memory of one CTA");
 };
@@ -100,15 +107,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_base - raw_addr);
     constexpr int LSTAGES = T::LOAD_STAGES;
-    const uint32_t a_base = smem_base;                                   // bf16 weight tiles (tile ring)
-    const uint32_t ld_base = a_base + STAGES * T::A_BYTES;               // load ring: [packed 16 KB][4 activation boxes]
+    const uint32_t a_base = smem_base;                                   // group ring: two bf16 tiles per slot
+    const uint32_t ld_base = a_base + STAGES * T::SLOT_BYTES;            // load ring: [packed 16 KB][4 activation boxes]
     const uint32_t bar_base = ld_base + LSTAGES * T::LOAD_STAGE_SMEM;
     auto landed_bar = [&](int s) { return bar_base + 8u * s; };
     auto lfree_bar = [&](int s) { return bar_base + 8u * (LSTAGES + s); };
     auto ready_bar = [&](int s) { return bar_base + 8u * (2 * LSTAGES + s); };
-    auto tfree_bar = [&](int s) { return bar_base + 8u * (2 * LSTAGES + STAGES + s); };
-    auto gfull_bar = [&](int b) { return bar_base + 8u * (2 * LSTAGES + 2 * STAGES + b); };
-    auto gempty_bar = [&](int b) { return bar_base + 8u * (2 * LSTAGES + 2 * STAGES + 2 + b); };
+    auto gdone_bar = [&](int s) { return bar_base + 8u * (2 * LSTAGES + STAGES + s); };
+    auto gempty_bar = [&](int s) { return bar_base + 8u * (2 * LSTAGES + 2 * STAGES + s); };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (bar_base - smem_base) + 8u * T::NUM_BARRIERS);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const uint8_t *ld_ptr = smem + (ld_base - smem_base);
@@ -120,15 +126,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < LSTAGES; s++) {
             mbar_init(landed_bar(s), 1);
-            mbar_init(lfree_bar(s), 1);
+            mbar_init(lfree_bar(s), 2);              // one commit per group of the stage (a lone group commits twice)
         }
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(ready_bar(s), 4);      // one arrival per warp of the dequantiser team that wrote the tile
-            mbar_init(tfree_bar(s), 1);
-        }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(gfull_bar(b), 1);
-            mbar_init(gempty_bar(b), 4);     // one arrival per fold warp
+            mbar_init(ready_bar(s), 4 * T::TEAMS);   // one arrival per dequantiser warp
+            mbar_init(gdone_bar(s), 1);
+            mbar_init(gempty_bar(s), 4);             // one arrival per fold warp
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -161,14 +164,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             bool ok = true;
             while (ok && sched.next(w)) {
                 const int n0 = w.tile * T::TILE_N;
-                const int item_kb = w.kb_count * T::GROUP_KB;
-                for (int kb = 0; kb < item_kb; kb += T::LOAD_KB, pcount++) {
+                for (int g = 0; g < w.kb_count; g += T::LOAD_GROUPS, pcount++) {
                     const int ps = pcount % LSTAGES;
                     if (!mbar_wait(lfree_bar(ps), (((uint32_t)(pcount / LSTAGES)) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, ps)) {
                         ok = false;
                         break;
                     }
-                    const int k0 = (w.kb_begin * T::GROUP_KB + kb) * T::BK;
+                    const int k0 = (w.kb_begin + g) * 128;
                     const uint32_t dst = ld_base + ps * T::LOAD_STAGE_SMEM;
                     // always the full 256-element box: past an item's end it brings unused (or zero-filled) data
                     mbar_arrive_expect_tx(landed_bar(ps), T::LOAD_TX_BYTES);
@@ -179,41 +181,46 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 1 || warp == 3) {
+        // ------------------------------------------------------------------ MMA issuers
         if (lane == 0) {
+            const int issuer = warp == 3 ? 1 : 0;
             const uint32_t instr = make_idesc(UMMA_BF16, UMMA_BF16, 128, MPAD);
-            int kcount = 0;          // k-blocks issued so far: tile ring slot kcount % STAGES
+            int gcount = 0;          // groups issued so far: ring slot gcount % STAGES
             int pcount = 0;          // load stages consumed so far
-            int giter = 0;           // groups issued so far: buffer giter & 1
             WorkSched<0> sched(cta, num_ctas, sp);
             WorkItem w;
             bool ok = true;
             while (ok && sched.next(w)) {
-                const int item_kb = w.kb_count * T::GROUP_KB;
-                for (int kb = 0; kb < item_kb && ok; kb++, kcount++) {
-                    const int j = kb % T::LOAD_KB;                 // k-block inside its load stage
+                for (int g = 0; g < w.kb_count; g++, gcount++) {
+                    const int slot = gcount % STAGES;
+                    const uint32_t sphase = ((uint32_t)(gcount / STAGES)) & 1u;
                     const int ps = pcount % LSTAGES;
-                    const int b = giter & 1;
-                    if (kb % T::GROUP_KB == 0) {
-                        if (!mbar_wait(gempty_bar(b), ((giter >> 1) & 1) ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, b)) { ok = false; break; }
-                        tc_fence_after_sync();
+                    const int jg = g % T::LOAD_GROUPS;             // group inside its load stage
+                    const bool stage_ends = (jg == T::LOAD_GROUPS - 1 || g == w.kb_count - 1);
+                    if ((gcount & 1) != issuer) {
+                        if (stage_ends) pcount++;
+                        continue;
                     }
-                    const int st = kcount % STAGES;
-                    // ready[st] also tells that the load stage has landed: the dequantisers waited for it
-                    if (!mbar_wait(ready_bar(st), ((uint32_t)(kcount / STAGES)) & 1u, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, st)) { ok = false; break; }
+                    if (!mbar_wait(gempty_bar(slot), sphase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, slot)) { ok = false; break; }
+                    // ready[slot] also tells that the load stage has landed: the dequantisers waited for it
+                    if (!mbar_wait(ready_bar(slot), sphase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, slot)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + (uint32_t)(b * MPAD);
-                    const uint64_t a_desc = make_smem_desc_k128(a_base + st * T::A_BYTES);
-                    const uint64_t b_desc = make_smem_desc_k128(ld_base + ps * T::LOAD_STAGE_SMEM + T::PACKED_BYTES + j * T::X_STRIDE);
-#ifndef W4_SKIP_MMA
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(slot * MPAD);
+                    const uint64_t a_desc = make_smem_desc_k128(a_base + slot * T::SLOT_BYTES);
+                    const uint64_t b_desc = make_smem_desc_k128(ld_base + ps * T::LOAD_STAGE_SMEM + T::PACKED_BYTES + jg * T::GROUP_KB * T::X_STRIDE);
 #pragma unroll
-                    for (int k = 0; k < 4; k++)
-                        umma_f16<1>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, (kb % T::GROUP_KB > 0 || k > 0) ? 1u : 0u);
-#endif
-                    umma_commit(tfree_bar(st));
-                    if (kb % T::GROUP_KB == T::GROUP_KB - 1) { umma_commit(gfull_bar(b)); giter++; }
-                    if (j == T::LOAD_KB - 1 || kb == item_kb - 1) { umma_commit(lfree_bar(ps)); pcount++; }
+                    for (int t = 0; t < T::GROUP_KB; t++) {
+                        // tile t of the group: next 16 KB of the slot, next activation box
+                        const uint64_t at = a_desc + (uint64_t)((t * T::A_BYTES) >> 4), bt = b_desc + (uint64_t)((t * T::X_STRIDE) >> 4);
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            umma_f16<1>(d_tmem, advance_desc_k(at, k), advance_desc_k(bt, k), instr, (t > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(gdone_bar(slot));
+                    umma_commit(lfree_bar(ps));
+                    if (stage_ends && jg == 0) umma_commit(lfree_bar(ps));   // the stage's only group: stand in for the missing one
+                    if (stage_ends) pcount++;
                 }
             }
         }
@@ -221,50 +228,47 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         // ------------------------------------------------------------------ dequantisers
         const int team = (warp - 8) >> 2;
         const int r = ((warp - 8) & 3) * 32 + lane;   // row of the tile this thread converts
-        int kcount = 0;                                // k-blocks seen so far (all teams count alike)
-        int pcount = 0;
+        int gcount = 0, pcount = 0;
         WorkSched<0> sched(cta, num_ctas, sp);
         WorkItem w;
         bool ok = true;
         while (ok && sched.next(w)) {
-            const int item_kb = w.kb_count * T::GROUP_KB;
-            for (int kb = 0; kb < item_kb; kb++, kcount++) {
-                const int j = kb % T::LOAD_KB;
+            for (int g = 0; g < w.kb_count; g++, gcount++) {
+                const int slot = gcount % STAGES;
+                const uint32_t sphase = ((uint32_t)(gcount / STAGES)) & 1u;
                 const int ps = pcount % LSTAGES;
                 const uint32_t pphase = ((uint32_t)(pcount / LSTAGES)) & 1u;
-                if (j == T::LOAD_KB - 1 || kb == item_kb - 1) pcount++;
-                if (kcount % T::TEAMS != team) continue;
-                const int st = kcount % STAGES;
+                const int jg = g % T::LOAD_GROUPS;
+                if (jg == T::LOAD_GROUPS - 1 || g == w.kb_count - 1) pcount++;
                 if (!mbar_wait(landed_bar(ps), pphase, abort_flag, p.status, ST_TIMEOUT_DEQUANT, ps)) { ok = false; break; }
-                if (!mbar_wait(tfree_bar(st), (((uint32_t)(kcount / STAGES)) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_DEQUANT, 16 + st)) { ok = false; break; }
-                // packed row r: 128 bytes, 128B-swizzled by the TMA; k-block j is its 16-byte chunks 2j and 2j+1
+                // the slot's tiles are free once the MMAs of the group that used it last are done
+                if (!mbar_wait(gdone_bar(slot), sphase ^ 1u, abort_flag, p.status, ST_TIMEOUT_DEQUANT, 16 + slot)) { ok = false; break; }
+                // packed row r: 128 bytes, 128B-swizzled by the TMA; k-block j of the stage is its 16-byte chunks 2j, 2j+1
                 const uint8_t *row = ld_ptr + ps * T::LOAD_STAGE_SMEM + r * 128;
-                const uint4 lo = *reinterpret_cast<const uint4 *>(row + (((2 * j) ^ (r & 7)) << 4));
-                const uint4 hi = *reinterpret_cast<const uint4 *>(row + (((2 * j + 1) ^ (r & 7)) << 4));
-                const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                const uint32_t dst_row = a_base + st * T::A_BYTES + r * 128;
-#ifndef W4_SKIP_DEQUANT
 #pragma unroll
-                for (int c = 0; c < 8; c++) {                      // 16-byte chunk c = k 8c .. 8c+7
-                    uint32_t o[4];
-                    int4x8_to_bf16x8(words[c], o);
-                    st_shared_v4(dst_row + (uint32_t)((c ^ (r & 7)) << 4), o[0], o[1], o[2], o[3]);
+                for (int t = team; t < T::GROUP_KB; t += T::TEAMS) {
+                    const int j = jg * T::GROUP_KB + t;
+                    const uint4 lo = *reinterpret_cast<const uint4 *>(row + (((2 * j) ^ (r & 7)) << 4));
+                    const uint4 hi = *reinterpret_cast<const uint4 *>(row + (((2 * j + 1) ^ (r & 7)) << 4));
+                    const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                    const uint32_t dst_row = a_base + slot * T::SLOT_BYTES + t * T::A_BYTES + r * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; c++) {                  // 16-byte chunk c = k 8c .. 8c+7
+                        uint32_t o[4];
+                        int4x8_to_bf16x8(words[c], o);
+                        st_shared_v4(dst_row + (uint32_t)((c ^ (r & 7)) << 4), o[0], o[1], o[2], o[3]);
+                    }
                 }
-#else
-                if (words[0] == 0x12345678u) st_shared_v4(dst_row, words[1], words[2], words[3], words[4]);
-#endif
-#ifndef W4_SKIP_FENCE
                 fence_proxy_async_smem();                         // make the writes visible to the tensor core's reads
-#endif
                 __syncwarp();
-                if (lane == 0) mbar_arrive(ready_bar(st));
+                if (lane == 0) mbar_arrive(ready_bar(slot));
             }
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ fold + epilogue
         const int q = warp - 4;                        // == warp % 4: the TMEM lane quarter of this warp
         const int r = q * 32 + lane;                   // weight row inside the tile = TMEM lane
-        int giter = 0;
+        int gcount = 0;
         WorkSched<0> sched(cta, num_ctas, sp);
         WorkItem w;
         bool ok = true;
@@ -285,12 +289,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     if (g0 + i >= w.kb_count) break;
-                    const int b = giter & 1;
+                    const int b = gcount % STAGES;
                     const float s = s_cur[i];
-                    if (!mbar_wait(gfull_bar(b), (giter >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, b)) { ok = false; break; }
+                    if (!mbar_wait(gdone_bar(b), (uint32_t)(gcount / STAGES) & 1u, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, b)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * MPAD);
-#ifndef W4_SKIP_FOLD
 #pragma unroll
                     for (int c0 = 0; c0 < MPAD; c0 += 16) {
                         uint32_t v[16];
@@ -299,13 +302,10 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 #pragma unroll
                         for (int e = 0; e < 16; e++) total[c0 + e] = fmaf(s, __uint_as_float(v[e]), total[c0 + e]);
                     }
-#else
-                    total[0] += s; (void)t_row;
-#endif
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(gempty_bar(b));
-                    giter++;
+                    gcount++;
                 }
 #pragma unroll
                 for (int i = 0; i < 8; i++) s_cur[i] = s_nxt[i];

@@ -62,11 +62,11 @@ class GemmConfig:
 
     def smem_bytes(self) -> int:
         """Dynamic shared memory of the kernel; must equal the traits' SMEM_ALLOC."""
-        if self.dt == "w4a16":   # W4A16Traits: bf16 tile ring (s stages) + load ring (16 KB packed + 4 activation boxes)
+        if self.dt == "w4a16":   # W4A16Traits: group ring (s slots of two bf16 tiles) + load ring (16 KB packed + 4 activation boxes)
             load_stage = 128 * 128 + 4 * (-(-self.bn * 128 // 1024) * 1024)
-            load_stages = min(4, (224 * 1024 - self.num_stages * 128 * 128) // load_stage)
-            return (self.num_stages * 128 * 128 + load_stages * load_stage
-                    + (2 * self.num_stages + 2 * load_stages + 4) * 8 + 16 + 1024)
+            load_stages = min(4, (224 * 1024 - self.num_stages * 2 * 128 * 128) // load_stage)
+            return (self.num_stages * 2 * 128 * 128 + load_stages * load_stage
+                    + (2 * load_stages + 3 * self.num_stages) * 8 + 16 + 1024)
         a = 128 * 128
         b = (self.bn // self.cg) * 128
         # block-scaled kinds stage one 512-byte scale atom per 128 rows and 128 K-elements
@@ -122,7 +122,7 @@ def generate_block_scaled(dt: str, max_smem: int) -> list[GemmConfig]:
 def generate_w4a16(max_smem: int) -> list[GemmConfig]:
     """W4A16 decode kernel: operands swapped (ab=1), bn = M padded to 16/32/64/128, stream-K work split."""
     out = []
-    for mpad, stage_opts in ((16, (4, 6)), (32, (4, 6)), (64, (3, 4)), (128, (2, 3))):
+    for mpad, stage_opts in ((16, (3, 4)), (32, (3, 4)), (64, (3, 4)), (128, (2,))):
         for st in stage_opts:
             c = GemmConfig("w4a16", 128, mpad, 64, st, 1, 0, 1, 0)
             if c.smem_bytes() <= max_smem:
