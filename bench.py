@@ -131,6 +131,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel", default=None, help="plugin configuration name (default: autotune cache, then built-in choice)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N>1: fused = epilogue TMA stores into every rank's Y over NVLink; nccl = all-gather + interleave kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -140,7 +142,7 @@ def main():
     import torch.distributed as dist
 
     import sm120_gemm_b200 as g
-    from sm120_gemm_b200.shard import NShardedGemm
+    from sm120_gemm_b200.shard import FusedNShardedGemm, NShardedGemm
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -152,6 +154,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer mappings only: no NVLink multicast objects
         dist.init_process_group("nccl", device_id=dev)
 
     reg = g.KernelRegistry()
@@ -205,7 +208,17 @@ def main():
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)      # every rank must make the same choice
         kern = cands[int(torch.argmin(t).item())]
-    op = NShardedGemm(kern, M, N, K, rank, world)
+    fused = world > 1 and args.gather == "fused" and kern.config.epi == 1 and kern.config.split_k == 1
+    if fused:
+        fop = FusedNShardedGemm(kern, M, N, K, rank, world)
+        Y = fop.Y
+
+        class _Op:
+            def run(self, X, W, Y):
+                return fop.run(X, W)
+        op = _Op()
+    else:
+        op = NShardedGemm(kern, M, N, K, rank, world)
 
     def barrier():
         if world > 1:
@@ -286,7 +299,9 @@ def main():
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "kernel": kern.config.name(), "l2": "inputs larger than L2 (X, W, Y = 1.5 GiB vs 126 MB L2)",
-                       "parallelism": "single GPU" if world == 1 else f"N-sharded x{world}: {plan_rows} weight rows per rank + NCCL all-gather + interleave"},
+                       "parallelism": "single GPU" if world == 1 else (
+                           f"N-sharded x{world}: {plan_rows} weight rows per rank, all-gather fused into the epilogue (TMA stores to every rank's Y over NVLink) + barrier"
+                           if fused else f"N-sharded x{world}: {plan_rows} weight rows per rank + NCCL all-gather + interleave")},
             "roofline": roofline,
             "e2e": {"value": flops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
                     "h2d_bytes_per_step": (M * K + plan_rows * K) * 2, "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps},

@@ -80,6 +80,15 @@ typedef struct GemmArgs {
     int32_t sm_limit;       /* 0 = all SMs; >0 = persistent grid uses at most this many    */
     int32_t reserved;
     gemm_stream_t stream;
+    /* N-sharded multi-GPU runs (TMA-store configurations only).  When y_num_peers > 0, Y is ignored and the   */
+    /* M x N result is stored into columns [y_col_offset, y_col_offset + N) of the row-major M x y_ld bf16     */
+    /* matrix at each of y_peers[0 .. y_num_peers-1]: device pointers this process can write, normally the     */
+    /* same symmetric buffer on every rank of the node, own rank included.  The stores are plain TMA stores    */
+    /* over NVLink; the caller orders them against readers (kernel completion on every rank, then a barrier).  */
+    int32_t y_num_peers;
+    int32_t y_col_offset;
+    int64_t y_ld;
+    void *y_peers[8];
 } GemmArgs;
 
 /*

@@ -46,6 +46,8 @@ class GemmArgs(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("sm_limit", ctypes.c_int32), ("reserved", ctypes.c_int32),
         ("stream", ctypes.c_void_p),
+        ("y_num_peers", ctypes.c_int32), ("y_col_offset", ctypes.c_int32), ("y_ld", ctypes.c_int64),
+        ("y_peers", ctypes.c_void_p * 8),
     ]
 
 

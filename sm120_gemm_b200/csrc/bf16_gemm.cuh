@@ -43,6 +43,21 @@ namespace sm100 {
 enum : int { OPK_BF16 = 0, OPK_E4M3 = 1, OPK_MXFP8 = 2, OPK_MXFP4 = 3 };
 enum : int { EPI_DIRECT = 0, EPI_TMA = 1 };     // epilogue: register->global stores, or smem + TMA store
 
+// Where the bf16 result goes.  Normally one row-major M x N matrix.  In an N-sharded multi-GPU run
+// each rank instead stores its M x N block into columns [col_offset, col_offset + N) of the row-major
+// M x ld result on EVERY rank (plain TMA stores through NVLink peer mappings; no multicast, no loads
+// from peer memory), which fuses the all-gather of the column blocks into the epilogue.
+static constexpr int MAX_Y_PEERS = 8;
+struct YMaps {
+    CUtensorMap m[MAX_Y_PEERS];
+};
+struct YTarget {
+    void *const *peers = nullptr;   // num_peers base pointers (this rank's own buffer among them); nullptr = plain Y
+    int num_peers = 0;
+    long long ld = 0;               // row pitch of the destination matrices in elements
+    int col_offset = 0;
+};
+
 struct GemmParams {
     int M, N, K;
     int num_m_blocks, num_n_blocks;
@@ -52,6 +67,8 @@ struct GemmParams {
     void *Y;              // bf16 output (direct epilogue)
     float *workspace;     // split-K partial sums [split][M][N]
     float alpha;          // epilogue scale (FP8 per-tensor: sx*sw)
+    int y_targets;        // TMA-store epilogue: destination matrices (1, or the ranks of a sharded run)
+    int y_col_offset;     // column of the destination where this GEMM's column 0 lands
     uint32_t *status;
     // block-scaled kinds: ue8m0 scale factors in 512-byte atoms of 128 rows x 4 K-blocks,
     // atom (row/128, kblock/4) at byte ((row/128) * sf_k_atoms + kblock/4) * 512
@@ -176,7 +193,7 @@ struct UmmaGemmTraits {
 template <class T>
 __global__ void __launch_bounds__(256, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                 const __grid_constant__ CUtensorMap tmap_y, const GemmParams p)
+                 const __grid_constant__ YMaps tmap_ys, const GemmParams p)
 {
     constexpr int CG = T::CG;
     constexpr int BN = T::BN;
@@ -219,7 +236,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         fence_proxy_async_smem();
         prefetch_tensormap(&tmap_x);
         prefetch_tensormap(&tmap_w);
-        if (T::EPI == EPI_TMA) prefetch_tensormap(&tmap_y);
+        if (T::EPI == EPI_TMA)
+            for (int t = 0; t < p.y_targets; t++) prefetch_tensormap(&tmap_ys.m[t]);
     }
     if (warp == 2) {
         tmem_alloc<CG>(smem_u32(tmem_slot), T::TMEM_COLS);
@@ -452,7 +470,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     fence_proxy_async_smem();
                     named_bar_sync(1, 128);
                     if (epi_tid == 0) {
-                        tma_store_2d(&tmap_y, stg, n0 + j * 64, m0);
+                        for (int t = 0; t < p.y_targets; t++) tma_store_2d(&tmap_ys.m[t], stg, p.y_col_offset + n0 + j * 64, m0);
                         tma_store_commit();
                     }
                     buf ^= 1;
@@ -684,10 +702,17 @@ struct UmmaGemmLauncher {
     }
 
     static int run(int M, int N, int K, const void *X, const void *W, void *Y, float *workspace, size_t workspace_bytes_given,
-                   float alpha, int sm_limit, cudaStream_t stream, const void *sf_x = nullptr, const void *sf_w = nullptr)
+                   float alpha, int sm_limit, cudaStream_t stream, const void *sf_x = nullptr, const void *sf_w = nullptr,
+                   const YTarget *yt = nullptr)
     {
         if (!can_run(M, N, K)) return set_error(GEMM_ERR_SHAPE, "shape %dx%dx%d not supported by this configuration", M, N, K);
-        if (!X || !W || !Y) return set_error(GEMM_ERR_ARG, "null operand pointer");
+        const bool fused_gather = yt != nullptr && yt->num_peers > 0;
+        if (fused_gather) {
+            if (T::EPI != EPI_TMA) return set_error(GEMM_ERR_ARG, "storing into peer matrices needs a TMA-store configuration (e1, no split-K)");
+            if (yt->num_peers > MAX_Y_PEERS || !yt->peers || yt->ld < yt->col_offset + (long long)N || yt->ld % 8 != 0 || yt->col_offset % 8 != 0)
+                return set_error(GEMM_ERR_ARG, "bad peer destination: %d peers, ld %lld, column offset %d", yt->num_peers, yt->ld, yt->col_offset);
+        }
+        if (!X || !W || (!Y && !fused_gather)) return set_error(GEMM_ERR_ARG, "null operand pointer");
         if (T::BLOCK_SCALED && (!sf_x || !sf_w)) return set_error(GEMM_ERR_ARG, "block-scaled configuration needs x_scale and w_scale");
         if (T::BLOCK_SCALED && ((reinterpret_cast<uintptr_t>(sf_x) | reinterpret_cast<uintptr_t>(sf_w)) & 15u))
             return set_error(GEMM_ERR_ARG, "scale arrays must be 16-byte aligned");
@@ -712,19 +737,31 @@ struct UmmaGemmLauncher {
         }
 
         const CUtensorMapDataType dt = (T::OPK == OPK_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-        CUtensorMap tx, tw, ty;
+        CUtensorMap tx, tw;
+        YMaps tys;
         const uint64_t row_bytes = (uint64_t)K * T::ELEM_BITS / 8;
         const uint64_t row_elems = (T::OPK == OPK_BF16) ? (uint64_t)K : row_bytes;   // fp8 / packed fp4 rows are mapped as bytes
         rc = make_tmap_2d(&tx, dt, X, row_elems, (uint64_t)M, row_bytes, T::BK_COORD, T::BM_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != GEMM_OK) return rc;
         rc = make_tmap_2d(&tw, dt, W, row_elems, (uint64_t)N, row_bytes, T::BK_COORD, T::BN_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != GEMM_OK) return rc;
-        if (T::EPI == EPI_TMA) {
-            rc = make_tmap_2d(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, Y, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, T::OUT_CHUNK, T::BM_CTA,
+        int y_targets = 1;
+        if (fused_gather) {
+            // one map per rank's matrix; the extent stops at this block's last column so that a partial last
+            // tile is clipped there and cannot spill into the next rank's columns
+            y_targets = yt->num_peers;
+            for (int t = 0; t < y_targets; t++) {
+                if (!yt->peers[t]) return set_error(GEMM_ERR_ARG, "null peer pointer %d", t);
+                rc = make_tmap_2d(&tys.m[t], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, yt->peers[t], (uint64_t)(yt->col_offset + N), (uint64_t)M,
+                                  (uint64_t)yt->ld * 2, T::OUT_CHUNK, T::BM_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
+                if (rc != GEMM_OK) return rc;
+            }
+        } else if (T::EPI == EPI_TMA) {
+            rc = make_tmap_2d(&tys.m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, Y, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, T::OUT_CHUNK, T::BM_CTA,
                               CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc != GEMM_OK) return rc;
         } else {
-            ty = tx;
+            tys.m[0] = tx;
         }
 
         GemmParams p;
@@ -738,6 +775,8 @@ struct UmmaGemmLauncher {
         p.workspace = workspace;
         p.alpha = alpha;
         p.status = dev->status;
+        p.y_targets = y_targets;
+        p.y_col_offset = fused_gather ? yt->col_offset : 0;
         p.sf_x = static_cast<const uint8_t *>(sf_x);
         p.sf_w = static_cast<const uint8_t *>(sf_w);
         p.sf_k_atoms = (K + 127) / 128;
@@ -759,7 +798,7 @@ struct UmmaGemmLauncher {
         attr.val.clusterDim.z = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
-        SM100_CUDA_TRY(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T>, tx, tw, ty, p));
+        SM100_CUDA_TRY(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T>, tx, tw, tys, p));
 
         if (T::SPLIT_K == 0) {
             const int tiles = p.num_m_blocks * p.num_n_blocks;

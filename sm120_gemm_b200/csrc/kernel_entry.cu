@@ -72,12 +72,18 @@ int gemm_run_ex(const GemmArgs *a)
     if (!a || a->struct_size != sizeof(GemmArgs)) return sm100::set_error(GEMM_ERR_ARG, "GemmArgs is null or has the wrong struct_size");
     if ((int)a->dtype != DT) return sm100::set_error(GEMM_ERR_ARG, "dtype %u does not match plugin %s", a->dtype, kConfigName);
 #if GEMM_DT == 3
+    if (a->y_num_peers > 0) return sm100::set_error(GEMM_ERR_ARG, "peer destinations are not supported by %s", kConfigName);
     return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, a->w_scale, a->group_size, static_cast<float *>(a->workspace), a->workspace_bytes,
                          a->sm_limit, a->stream);
 #else
     const float alpha = (DT == GEMM_DT_FP8) ? a->x_scale_f * a->w_scale_f : 1.0f;
+    sm100::YTarget yt;
+    yt.peers = a->y_peers;
+    yt.num_peers = a->y_num_peers;
+    yt.ld = a->y_ld;
+    yt.col_offset = a->y_col_offset;
     return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, static_cast<float *>(a->workspace), a->workspace_bytes, alpha,
-                         a->sm_limit, a->stream, a->x_scale, a->w_scale);
+                         a->sm_limit, a->stream, a->x_scale, a->w_scale, a->y_num_peers > 0 ? &yt : nullptr);
 #endif
 }
 

@@ -40,6 +40,53 @@ def blocked_to_row_major_index(plan_world: int, M: int, nb: int, m: int, n: int)
     return (r * M + m) * nb + j
 
 
+class FusedNShardedGemm:
+    """Per-rank GEMM whose epilogue stores its column block straight into the row-major Y of every
+    rank (TMA stores over NVLink into a symmetric buffer), so the all-gather overlaps the math tile by
+    tile and no interleave pass is needed.  ``run`` ends with a cross-rank barrier on the stream: after
+    it, this rank's Y holds every rank's block.  Needs a TMA-store configuration (``e1``, no split-K)."""
+
+    def __init__(self, kernel, M: int, N: int, K: int, rank: int, world: int, group=None):
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import GemmArgs
+
+        if kernel.config.epi != 1 or kernel.config.split_k != 1:
+            raise ValueError(f"{kernel.config.name()} has no TMA-store epilogue")
+        self.torch = torch
+        self.kernel = kernel
+        self.M, self.N, self.K = M, N, K
+        self.plan = shard_plan(N, world, rank)
+        if not kernel.can_run(M, self.plan.rows, K):
+            raise ValueError(f"{kernel.config.name()} cannot run the {M}x{self.plan.rows}x{K} shard")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.Y = symm_mem.empty((M, N), dtype=torch.bfloat16, device=dev)       # same buffer on every rank
+        self.handle = symm_mem.rendezvous(self.Y, group if group is not None else dist.group.WORLD)
+        ptrs = list(self.handle.buffer_ptrs)
+        assert len(ptrs) == world <= 8
+        a = GemmArgs()
+        a.M, a.N, a.K = M, self.plan.rows, K
+        a.x_scale_f = a.w_scale_f = 1.0
+        a.y_num_peers, a.y_col_offset, a.y_ld = world, self.plan.row_start, N
+        for i, ptr in enumerate(ptrs):
+            a.y_peers[i] = ptr
+        self.args = a
+
+    def run(self, X, W_shard):
+        from . import dispatch_ex
+
+        a = self.args
+        a.X, a.W = X.data_ptr(), W_shard.data_ptr()
+        a.stream = self.torch.cuda.current_stream().cuda_stream
+        dispatch_ex(self.kernel, a)
+        self.handle.barrier()          # every rank's stores have landed before anyone reads Y
+        return 1
+
+
 class NShardedGemm:
     """Per-rank GEMM + all-gather + interleave on the current CUDA device.
 

@@ -186,3 +186,35 @@ def test_oracle_agrees_with_reference_check_kernel(cuda_device):
     # same k-ascending FP32 loop; the only freedom is FMA contraction
     assert np.abs(got - strict).max() <= 1e-5 * max(1.0, np.abs(strict).max())
     assert np.abs(got - fast).max() <= 1e-4 * max(1.0, np.abs(strict).max())
+
+
+def test_peer_destination_epilogue_single_gpu(registry, cuda_device):
+    """The fused all-gather epilogue, exercised on one GPU: two destination matrices (stand-ins for two
+    ranks' Y) each receive this GEMM's block at a column offset of a wider row-major matrix; columns
+    outside the block must stay untouched, also when the block's last tile is partial."""
+    import ctypes
+
+    import sm120_gemm_b200 as g
+
+    k = registry.find(BEST)
+    M, Nb, K, ld, off = 300, 328, 512, 1024, 256          # 328 = 256 + 72: partial last tile inside the destination
+    X, W = o.make_inputs(M, Nb, K, seed=11)
+    ref = o.gemm_bf16(X, W)
+    Xd, Wd = to_dev(X), to_dev(W)
+    dst = [torch.full((M, ld), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    a = g.GemmArgs()
+    a.M, a.N, a.K = M, Nb, K
+    a.X, a.W = Xd.data_ptr(), Wd.data_ptr()
+    a.x_scale_f = a.w_scale_f = 1.0
+    a.y_num_peers, a.y_col_offset, a.y_ld = 2, off, ld
+    a.y_peers[0], a.y_peers[1] = dst[0].data_ptr(), dst[1].data_ptr()
+    a.stream = torch.cuda.current_stream().cuda_stream
+    g.dispatch_ex(k, a)
+    torch.cuda.synchronize()
+    k.check_status()
+    for d in dst:
+        dense_ok(to_bits(d[:, off:off + Nb].contiguous()), ref, X, W, K)
+        assert torch.all(d[:, :off] == 7.0) and torch.all(d[:, off + Nb:] == 7.0)
+    sk = registry.find("bf16_bm128_bn128_bk64_s7_cg1_sk4_ab0_e0")
+    with pytest.raises(g.GemmError):
+        g.dispatch_ex(sk, a)                                # split-K plugins cannot store to peers
