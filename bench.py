@@ -28,7 +28,7 @@ WORKLOAD = "bf16 gemm Y=X*W^T M=N=K=16384, X,W~N(0,1) seed 2, fp32 accumulate, b
 DEFAULT_KERNEL = "bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel at this workload,
 # from the ncu capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES = None
+NCU_TRAFFIC_BYTES = 13662148608 + 537297664   # profiles/kernel_families_limited_metrics.md, 16384^3 row
 
 
 def load_peaks():
