@@ -218,3 +218,23 @@ def test_peer_destination_epilogue_single_gpu(registry, cuda_device):
     sk = registry.find("bf16_bm128_bn128_bk64_s7_cg1_sk4_ab0_e0")
     with pytest.raises(g.GemmError):
         g.dispatch_ex(sk, a)                                # split-K plugins cannot store to peers
+
+
+def test_host_buffer_gemm_chunked_pipeline(registry, cuda_device):
+    """HostGemm (pinned host buffers in and out, copies and kernel overlapped by row chunks) equals the
+    device-resident call bit for bit, including a ragged last chunk."""
+    from sm120_gemm_b200.host_gemm import HostGemm
+
+    k = registry.find(BEST)
+    M, N, K = 1000, 768, 640
+    X, W = o.make_inputs(M, N, K, seed=13)
+    Xh = torch.from_numpy(X.view(np.int16)).view(torch.bfloat16).pin_memory()
+    Wh = torch.from_numpy(W.view(np.int16)).view(torch.bfloat16).pin_memory()
+    Yh = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    hg = HostGemm(k, M, N, K, chunk_rows=384)
+    assert hg.run(Xh, Wh, Yh) == 3
+    torch.cuda.synchronize()
+    k.check_status()
+    expect = run_bf16(k, to_dev(X), to_dev(W))
+    assert torch.equal(Yh.cuda(), expect)
+    dense_ok(to_bits(Yh.cuda()), o.gemm_bf16(X, W), X, W, K)
