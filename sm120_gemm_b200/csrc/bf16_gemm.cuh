@@ -72,7 +72,6 @@ struct GemmParams {
     uint32_t *status;
     // block-scaled kinds: ue8m0 scale factors in 512-byte atoms of 128 rows x 4 K-blocks,
     // atom (row/128, kblock/4) at byte ((row/128) * sf_k_atoms + kblock/4) * 512
-    const uint8_t *sf_x, *sf_w;
     int sf_k_atoms;
 };
 
@@ -179,21 +178,25 @@ struct UmmaGemmTraits {
     static constexpr int ACC_STAGES = (2 * ACC_STRIDE + SF_COLS <= 512) ? 2 : 1;
     static constexpr int ACC_COLS = ACC_STAGES * ACC_STRIDE + SF_COLS;
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
-    static constexpr int THREADS = 256;
+    // Kernels with a single accumulator buffer cannot hide the epilogue behind the next main loop, so they
+    // drain it with two epilogue groups of four warps (alternate 64- or 16-column pieces) instead of one.
+    static constexpr int EPI_GROUPS = ACC_STAGES == 1 ? 2 : 1;
+    static constexpr int THREADS = 128 + 128 * EPI_GROUPS;
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "BN (the UMMA N extent) is a multiple of 16 up to 256");
     static_assert(EPI != EPI_TMA || BN_ % 64 == 0, "the TMA-store epilogue writes 64-column boxes");
     static_assert((BN_ / CG_) % 8 == 0, "each CTA loads whole 8-row swizzle groups of W");
     static_assert(CG_ == 1 || CG_ == 2, "CTA group is 1 or 2");
     static_assert(STAGES_ >= 2, "at least two ring stages");
-    static_assert(!BLOCK_SCALED || (CG_ == 1 && BN_ % 128 == 0), "block-scaled tiles: one CTA, BN a multiple of the 128-row scale atom");
+    static_assert(!BLOCK_SCALED || BN_ % 128 == 0, "block-scaled tiles: BN a multiple of the 128-row scale atom");
     static_assert(ACC_COLS <= 512, "TMEM has 512 columns");
     static_assert(SMEM_ALLOC <= 232448, "exceeds the 227 KB of shared memory one CTA can have");
 };
 
 template <class T>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(T::THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                 const __grid_constant__ YMaps tmap_ys, const GemmParams p)
+                 const __grid_constant__ YMaps tmap_ys, const __grid_constant__ CUtensorMap tmap_sfx,
+                 const __grid_constant__ CUtensorMap tmap_sfw, const GemmParams p)
 {
     constexpr int CG = T::CG;
     constexpr int BN = T::BN;
@@ -229,7 +232,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), CG * 4);   // one arrival per epilogue warp of every CTA of the group
+            mbar_init(tempty_bar(a), CG * 4 * T::EPI_GROUPS);   // one arrival per epilogue warp of every CTA of the group
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -250,6 +253,27 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     // split-K / stream-K: the reduce kernel that follows may be scheduled from now on (it blocks
     // in griddepcontrol.wait until this grid has finished)
     if constexpr (T::SPLIT_K != 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // Scale atoms of one k-block: this CTA's 128 X rows, then every 128-row group of the tile's W rows (a CTA
+    // pair computes all BN columns in each CTA, so each CTA fetches all of them).  The tiled scale array is
+    // mapped as rows of 256 bytes, two per 512-byte atom.
+    auto load_scale_atoms = [&](int stage, int kblock, int row_x, int row_w_tile, uint32_t bar) {
+        const uint32_t sf_dst = sf_base + stage * T::SF_BYTES;
+        const int katom = kblock * T::SF_K_ATOMS;
+#pragma unroll
+        for (int a = 0; a < T::SF_K_ATOMS; a++) {
+            const int ax = ((row_x / 128) * p.sf_k_atoms + katom + a) * 2;
+            if constexpr (CG == 1) tma_load_2d(sf_dst + a * 512, &tmap_sfx, bar, 0, ax);
+            else tma_load_2d_pair(sf_dst + a * 512, &tmap_sfx, bar, 0, ax);
+#pragma unroll
+            for (int j = 0; j < T::SF_N_ATOMS; j++) {
+                const int aw = ((row_w_tile / 128 + j) * p.sf_k_atoms + katom + a) * 2;
+                const uint32_t dst = sf_dst + T::SF_A_BYTES + (a * T::SF_N_ATOMS + j) * 512;
+                if constexpr (CG == 1) tma_load_2d(dst, &tmap_sfw, bar, 0, aw);
+                else tma_load_2d_pair(dst, &tmap_sfw, bar, 0, aw);
+            }
+        }
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -288,25 +312,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                             mbar_arrive_expect_tx(full_bar(stage), T::STAGE_BYTES);
                             tma_load_2d(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w);
                             tma_load_2d(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x);
-                            if constexpr (T::BLOCK_SCALED) {
-                                // scale atoms of this k-block: X rows first, then one per 128 W rows
-                                const uint32_t sf_dst = sf_base + stage * T::SF_BYTES;
-                                const size_t katom = (size_t)(kb0 + kb + d) * T::SF_K_ATOMS;
-#pragma unroll
-                                for (int a = 0; a < T::SF_K_ATOMS; a++) {
-                                    bulk_load(sf_dst + a * 512, p.sf_x + ((size_t)(row_x / 128) * p.sf_k_atoms + katom + a) * 512, 512,
-                                              full_bar(stage));
-#pragma unroll
-                                    for (int j = 0; j < T::SF_N_ATOMS; j++)
-                                        bulk_load(sf_dst + T::SF_A_BYTES + (a * T::SF_N_ATOMS + j) * 512,
-                                                  p.sf_w + ((size_t)(row_w / 128 + j) * p.sf_k_atoms + katom + a) * 512, 512, full_bar(stage));
-                                }
-                            }
+                            if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, kb0 + kb + d, row_x, nb * BN, full_bar(stage));
                         } else {
                             if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
                             const uint32_t fb = full_leader + 8u * stage;
                             tma_load_2d_pair(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w);
                             tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x);
+                            if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, kb0 + kb + d, row_x, nb * BN, fb);
                         }
                         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                     }
@@ -315,7 +327,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0 && cta_rank == 0) {
+        if (cta_rank == 0) {   // every lane runs the loop; one elected lane issues (see elect_one_sync)
             const uint32_t instr = (T::OPK == OPK_BF16) ? make_idesc(UMMA_BF16, UMMA_BF16, T::BM, BN)
                                                          : make_idesc(UMMA_E4M3, UMMA_E4M3, T::BM, BN);
             // scale factors live behind the accumulator buffers: X atoms, then W atoms
@@ -330,25 +342,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             for (; ok && sched.next(w); titer++) {
                 const int acc = titer % T::ACC_STAGES;
                 const uint32_t acc_phase = (titer / T::ACC_STAGES) & 1;
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, acc)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, acc))) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * T::ACC_STRIDE);
                 for (int kb = 0; kb < w.kb_count; kb++) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage))) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
+                    if (elect_one_sync()) {
                     const uint64_t a_desc = make_smem_desc_k128(a_base + stage * T::A_BYTES);
                     const uint64_t b_desc = make_smem_desc_k128(b_base + stage * T::B_BYTES);
                     if constexpr (T::BLOCK_SCALED) {
                         const uint32_t sf_src = sf_base + stage * T::SF_BYTES;
 #pragma unroll
                         for (int a = 0; a < T::SF_K_ATOMS; a++) {
-                            tmem_cp_sf_atom(sfa_tmem + a * 4, make_sf_atom_desc(sf_src + a * 512));
+                            tmem_cp_sf_atom<CG>(sfa_tmem + a * 4, make_sf_atom_desc(sf_src + a * 512));
 #pragma unroll
                             for (int j = 0; j < T::SF_N_ATOMS; j++)
-                                tmem_cp_sf_atom(sfb_tmem + (a * T::SF_N_ATOMS + j) * 4,
+                                tmem_cp_sf_atom<CG>(sfb_tmem + (a * T::SF_N_ATOMS + j) * 4,
                                                 make_sf_atom_desc(sf_src + T::SF_A_BYTES + (a * T::SF_N_ATOMS + j) * 512));
                         }
                     }
@@ -357,11 +370,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
                         if constexpr (T::OPK == OPK_MXFP8) {
                             // 4 instructions of 32 K-elements share one atom: instruction k uses scale byte k
-                            umma_mxf8(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k),
+                            umma_mxf8<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k),
                                       make_idesc_block_scaled(UMMA_E4M3, UMMA_E4M3, T::BM, BN, k, k), sfa_tmem, sfb_tmem, accumulate);
                         } else if constexpr (T::OPK == OPK_MXFP4) {
                             // 4 instructions of 64 K-elements: two per atom, each using one half (2 scale bytes)
-                            umma_mxf4(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k),
+                            umma_mxf4<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k),
                                       make_idesc_block_scaled(UMMA_MXF4_E2M1, UMMA_MXF4_E2M1, T::BM, BN, (k & 1) * 2, (k & 1) * 2),
                                       sfa_tmem + (k >> 1) * 4, sfb_tmem + (k >> 1) * (T::SF_N_ATOMS * 4), accumulate);
                         } else
@@ -371,17 +384,25 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                             umma_f8f6f4<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, accumulate);
                     }
                     if constexpr (CG == 1) umma_commit(empty_bar(stage)); else umma_commit_pair(empty_bar(stage), 3);
+                    }
+                    __syncwarp();
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                if constexpr (CG == 1) umma_commit(tfull_bar(acc)); else umma_commit_pair(tfull_bar(acc), 3);
+                if (elect_one_sync()) {
+                    if constexpr (CG == 1) umma_commit(tfull_bar(acc)); else umma_commit_pair(tfull_bar(acc), 3);
+                }
+                __syncwarp();
             }
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ epilogue
-        const int q = warp - 4;                    // TMEM lane quarter this warp may read
+        constexpr int EG = T::EPI_GROUPS;
+        const int eg = (warp - 4) >> 2;            // epilogue group of this warp
+        const int q = (warp - 4) & 3;              // == warp % 4: the TMEM lane quarter this warp may read
         const int row_in_tile = q * 32 + lane;     // accumulator row = TMEM lane
-        const int epi_tid = threadIdx.x - 128;
+        const int epi_tid = threadIdx.x - 128 - eg * 128;
+        const uint32_t bar_a = 1 + 2 * eg, bar_b = 2 + 2 * eg;   // named barriers of this group
         const uint32_t tempty_leader = (CG == 2) ? mapa_shared(tempty_bar(0), 0) : tempty_bar(0);
         int titer = 0;
         int buf = 0;
@@ -397,7 +418,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             // all 128 epilogue threads must take the same decision, or the ones that go on would
             // wait at a named barrier for the ones that left
             const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, acc);
-            if (!named_bar_and(2, 128, got)) break;
+            if (!named_bar_and(bar_b, 128, got)) break;
             tc_fence_after_sync();
             const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * T::ACC_STRIDE);
             const int grow = m0 + row_in_tile;
@@ -415,7 +436,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 // stream-K partial: the CTA's private slot, tile-local [BM][BN] layout, no bounds
                 float *slot = p.workspace + ((size_t)(2 * cluster_id + w.part) * T::BM + cta_rank * T::BM_CTA + row_in_tile) * BN;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = eg * 16; c0 < BN; c0 += 16 * EG) {
                     uint32_t r[16];
                     tmem_ld_32x16(t_row + (uint32_t)c0, r);
                     tmem_ld_wait();
@@ -427,7 +448,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             } else if constexpr (T::SPLIT_K > 1) {
                 // FP32 partial of this K slice into workspace[split][M][N]
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = eg * 16; c0 < BN; c0 += 16 * EG) {
                     uint32_t r[16];
                     tmem_ld_32x16(t_row + (uint32_t)c0, r);
                     tmem_ld_wait();
@@ -443,11 +464,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             } else if constexpr (T::EPI == EPI_TMA) {
                 // bf16 through swizzled shared memory and TMA stores of 128 x 64 boxes
 #pragma unroll 1
-                for (int j = 0; j < BN / 64; j++) {
-                    // the store that last read this staging buffer must have finished reading it
-                    if (epi_tid == 0) tma_store_wait_read<1>();
-                    named_bar_sync(1, 128);
-                    const uint32_t stg = stg_base + buf * (T::BM_CTA * 128);
+                for (int j = eg; j < BN / 64; j += EG) {
+                    // the store that last read this staging buffer must have finished reading it (one group:
+                    // two buffers in turn; two groups: one buffer each)
+                    if (epi_tid == 0) { if constexpr (EG == 1) tma_store_wait_read<1>(); else tma_store_wait_read<0>(); }
+                    named_bar_sync(bar_a, 128);
+                    const uint32_t stg = stg_base + (EG == 1 ? buf : eg) * (T::BM_CTA * 128);
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         uint32_t r[32];
@@ -466,9 +488,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                             st_shared_v4(stg + row_in_tile * 128 + chunk * 16, pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
                         }
                     }
-                    if (j == BN / 64 - 1) release_acc();
+                    if (j + EG >= BN / 64) release_acc();       // this group's last piece of the accumulator
                     fence_proxy_async_smem();
-                    named_bar_sync(1, 128);
+                    named_bar_sync(bar_a, 128);
                     if (epi_tid == 0) {
                         for (int t = 0; t < p.y_targets; t++) tma_store_2d(&tmap_ys.m[t], stg, p.y_col_offset + n0 + j * 64, m0);
                         tma_store_commit();
@@ -478,7 +500,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             } else {
                 // bf16 straight from registers: 32 bytes per thread and step
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = eg * 16; c0 < BN; c0 += 16 * EG) {
                     uint32_t r[16];
                     tmem_ld_32x16(t_row + (uint32_t)c0, r);
                     tmem_ld_wait();
@@ -745,6 +767,16 @@ struct UmmaGemmLauncher {
         if (rc != GEMM_OK) return rc;
         rc = make_tmap_2d(&tw, dt, W, row_elems, (uint64_t)N, row_bytes, T::BK_COORD, T::BN_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != GEMM_OK) return rc;
+        CUtensorMap tsfx = tx, tsfw = tx;   // placeholders unless block-scaled
+        if (T::BLOCK_SCALED) {
+            const uint64_t k_atoms = ((uint64_t)K + 127) / 128;
+            rc = make_tmap_2d(&tsfx, CU_TENSOR_MAP_DATA_TYPE_UINT8, sf_x, 256, ((uint64_t)M + 127) / 128 * k_atoms * 2, 256, 256, 2,
+                              CU_TENSOR_MAP_SWIZZLE_NONE);
+            if (rc != GEMM_OK) return rc;
+            rc = make_tmap_2d(&tsfw, CU_TENSOR_MAP_DATA_TYPE_UINT8, sf_w, 256, ((uint64_t)N + 127) / 128 * k_atoms * 2, 256, 256, 2,
+                              CU_TENSOR_MAP_SWIZZLE_NONE);
+            if (rc != GEMM_OK) return rc;
+        }
         int y_targets = 1;
         if (fused_gather) {
             // one map per rank's matrix; the extent stops at this block's last column so that a partial last
@@ -777,8 +809,6 @@ struct UmmaGemmLauncher {
         p.status = dev->status;
         p.y_targets = y_targets;
         p.y_col_offset = fused_gather ? yt->col_offset : 0;
-        p.sf_x = static_cast<const uint8_t *>(sf_x);
-        p.sf_w = static_cast<const uint8_t *>(sf_w);
         p.sf_k_atoms = (K + 127) / 128;
         const long long work = (long long)p.num_m_blocks * p.num_n_blocks * (T::SPLIT_K > 0 ? T::SPLIT_K : p.num_k_blocks);
         int grid = 0;
@@ -798,7 +828,7 @@ struct UmmaGemmLauncher {
         attr.val.clusterDim.z = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
-        SM100_CUDA_TRY(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T>, tx, tw, tys, p));
+        SM100_CUDA_TRY(cudaLaunchKernelEx(&cfg, umma_gemm_kernel<T>, tx, tw, tys, tsfx, tsfw, p));
 
         if (T::SPLIT_K == 0) {
             const int tiles = p.num_m_blocks * p.num_n_blocks;

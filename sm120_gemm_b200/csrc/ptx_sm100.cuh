@@ -215,6 +215,18 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map)
 }
 
 // ---------------------------------------------------------------------------------- tcgen05
+// One lane of a fully active warp.  The tcgen05 issue loops run on ALL lanes of their warp with
+// warp-uniform control flow and only the instructions themselves sit under this predicate: the
+// descriptors are then warp-uniform values the compiler can keep in uniform registers, which is
+// where tcgen05 instructions take their operands from.  (A loop run by a single diverged thread
+// has to move every operand into uniform registers per instruction, ~60-80 cycles each.)
+__device__ __forceinline__ bool elect_one_sync()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 template <int CG>
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols)
 {
@@ -290,33 +302,54 @@ __device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, ui
 
 // Block-scaled MMAs (one CTA): D (+)= (A * SFA) * (B * SFB), ue8m0 scale factors read from TMEM.
 // mxf8f6f4: one scale per 32 K-elements, 32 K-elements per instruction (scale_vec::1X).
+template <int CG>
 __device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
                                           uint32_t sfb_tmem, uint32_t accumulate)
 {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
-        : "memory");
+    if constexpr (CG == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
 }
 
 // mxf4: e2m1 elements, one scale per 32 K-elements, 64 K-elements per instruction (scale_vec::2X).
+template <int CG>
 __device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
                                           uint32_t sfb_tmem, uint32_t accumulate)
 {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
-        : "memory");
+    if constexpr (CG == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
 }
 
 // Shared memory -> TMEM copy of one 512-byte scale-factor atom: 32 rows x 16 bytes, written
 // to 4 TMEM columns of lanes 0..31 and replicated into the other three lane quarters (the
-// form the block-scaled MMA reads).  Issued by one thread, ordered with its later MMAs.
+// form the block-scaled MMA reads).  Issued by one thread, ordered with its later MMAs.  For a CTA
+// pair one instruction makes each CTA copy from ITS OWN shared memory into ITS OWN TMEM.
+template <int CG>
 __device__ __forceinline__ void tmem_cp_sf_atom(uint32_t taddr, uint64_t smem_desc)
 {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+    if constexpr (CG == 1)
+        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+    else
+        asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
 }
 
 // Untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), completion counted

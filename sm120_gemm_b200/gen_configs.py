@@ -108,9 +108,12 @@ def max_stages(dt: str, bn: int, cg: int, sk: int, epi: int, cap: int = MAX_SMEM
 
 
 def generate_block_scaled(dt: str, max_smem: int) -> list[GemmConfig]:
-    """MXFP8 / MX-FP4: one CTA per tile, BN a multiple of the 128-row scale atom."""
+    """MXFP8 / MX-FP4: BN a multiple of the 128-row scale atom; one CTA or a CTA pair per tile."""
     bk = 128 * 8 // ELEM_BITS[dt]
     out = []
+    for bn in (128, 256):
+        for epi in (1, 0):
+            out.append(GemmConfig(dt, 256, bn, bk, min(max_stages(dt, bn, 2, 1, epi, max_smem), 8), 2, 1, 0, epi))
     for bn in (128, 256):
         for epi in (1, 0):
             out.append(GemmConfig(dt, 128, bn, bk, min(max_stages(dt, bn, 1, 1, epi, max_smem), 8), 1, 1, 0, epi))
