@@ -64,6 +64,7 @@ struct GemmParams {
     int num_k_blocks;     // per split (stream-K: per tile)
     int group_n;          // width (in N tiles) of a rasterisation band
     int burst;            // k-blocks the producer requests together (1 .. STAGES)
+    int l2_hint;          // 1: W loads evict-last, X loads evict-first (keeps a band of W panels in L2 while X streams)
     void *Y;              // bf16 output (direct epilogue)
     float *workspace;     // split-K partial sums [split][M][N]
     float alpha;          // epilogue scale (FP8 per-tensor: sx*sw)
@@ -281,6 +282,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             const uint32_t full_leader = (CG == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
+            const uint64_t pol_w = l2_policy_evict_last(), pol_x = l2_policy_evict_first();
             bool ok = true;
             WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
             WorkItem w;
@@ -310,14 +312,24 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         const int kx = (kb0 + kb + d) * T::BK_COORD;
                         if constexpr (CG == 1) {
                             mbar_arrive_expect_tx(full_bar(stage), T::STAGE_BYTES);
+                            if (p.l2_hint) {
+                                tma_load_2d_hint(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w, pol_w);
+                                tma_load_2d_hint(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x, pol_x);
+                            } else {
                             tma_load_2d(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w);
                             tma_load_2d(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x);
+                            }
                             if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, kb0 + kb + d, row_x, nb * BN, full_bar(stage));
                         } else {
                             if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
                             const uint32_t fb = full_leader + 8u * stage;
+                            if (p.l2_hint) {
+                                tma_load_2d_pair_hint(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w, pol_w);
+                                tma_load_2d_pair_hint(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x, pol_x);
+                            } else {
                             tma_load_2d_pair(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w);
                             tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x);
+                            }
                             if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, kb0 + kb + d, row_x, nb * BN, fb);
                         }
                         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -640,6 +652,18 @@ inline cudaLaunchConfig_t dependent_launch_config(unsigned blocks, unsigned thre
     return cfg;
 }
 
+// L2 cache hints on the operand loads.  SM100_GEMM_L2HINT=0/1 overrides (tuning runs).
+inline int l2_hint_mode(int M, int N, int K)
+{
+    static const int override_h = []() {
+        const char *e = std::getenv("SM100_GEMM_L2HINT");
+        return e ? std::atoi(e) : -1;
+    }();
+    if (override_h >= 0) return override_h;
+    (void)M; (void)N; (void)K;
+    return 0;
+}
+
 // k-blocks requested together by the TMA producer.  SM100_GEMM_BURST overrides (tuning runs).
 inline int load_burst(int stages)
 {
@@ -803,6 +827,7 @@ struct UmmaGemmLauncher {
         p.num_k_blocks = ((K + T::BK - 1) / T::BK) / (T::SPLIT_K > 0 ? T::SPLIT_K : 1);
         p.group_n = band_width(T::BN);
         p.burst = load_burst(T::STAGES);
+        p.l2_hint = l2_hint_mode(M, N, K);
         p.Y = Y;
         p.workspace = workspace;
         p.alpha = alpha;
