@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the hot path: BF16 Y = X * W^T, M = N = K = 16384 (BASELINE config 3), FP32
-accumulate, on N GPUs of one node.  At N > 1 the weight rows are sharded (N/g per rank) and
-one NCCL all-gather collects the bf16 column blocks of Y; total work is fixed (strong scaling).
+accumulate, on N GPUs of one node.  At N > 1 the weight rows are sharded (N/g per rank) and the
+bf16 column blocks of Y are all-gathered, by default inside the GEMM epilogue (stores over NVLink
+into every rank's Y) or with --gather nccl by one NCCL all-gather; total work is fixed (strong scaling).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -132,7 +133,8 @@ def main():
     ap.add_argument("--kernel", default=None, help="plugin configuration name (default: autotune cache, then built-in choice)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
-                    help="N>1: fused = epilogue TMA stores into every rank's Y over NVLink; nccl = all-gather + interleave kernel")
+                    help="N>1: fused = the epilogue stores into every rank's Y over NVLink (multimem stores to the NVSwitch multicast "
+                         "address when the node offers one, else one TMA store per peer); nccl = all-gather + interleave kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -154,7 +156,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer mappings only: no NVLink multicast objects
+        # the fused gather stores to the NVSwitch multicast mapping of Y when symmetric memory offers one
+        # (TORCH_SYMM_MEM_DISABLE_MULTICAST=1 or SM100_GEMM_MULTICAST=0 selects one TMA store per peer instead)
         dist.init_process_group("nccl", device_id=dev)
 
     reg = g.KernelRegistry()
@@ -316,7 +319,8 @@ def main():
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "kernel": kern.config.name(), "l2": "inputs larger than L2 (X, W, Y = 1.5 GiB vs 126 MB L2)",
                        "parallelism": "single GPU" if world == 1 else (
-                           f"N-sharded x{world}: {plan_rows} weight rows per rank, all-gather fused into the epilogue (TMA stores to every rank's Y over NVLink) + barrier"
+                           f"N-sharded x{world}: {plan_rows} weight rows per rank, all-gather fused into the epilogue "
+                           + ("(multimem stores to the NVSwitch multicast address of Y)" if fop.multicast else "(TMA stores to every rank's Y over NVLink)") + " + barrier"
                            if fused else f"N-sharded x{world}: {plan_rows} weight rows per rank + NCCL all-gather + interleave")},
             "roofline": roofline,
             "e2e": {"value": flops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",

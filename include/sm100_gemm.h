@@ -89,6 +89,11 @@ typedef struct GemmArgs {
     int32_t y_col_offset;
     int64_t y_ld;
     void *y_peers[8];
+    /* Optional.  Multicast (NVSwitch) address of that same symmetric matrix: a store to it lands in every     */
+    /* rank's copy.  When non-NULL the epilogue issues one multimem store per 16 bytes instead of one TMA      */
+    /* store per peer, so each result byte leaves this GPU once; y_num_peers must still be > 0 and N a         */
+    /* multiple of 8.  Every process bound to the multicast object must stay alive until the stores are done.  */
+    void *y_multicast;
 } GemmArgs;
 
 /*

@@ -47,7 +47,7 @@ class GemmArgs(ctypes.Structure):
         ("sm_limit", ctypes.c_int32), ("reserved", ctypes.c_int32),
         ("stream", ctypes.c_void_p),
         ("y_num_peers", ctypes.c_int32), ("y_col_offset", ctypes.c_int32), ("y_ld", ctypes.c_int64),
-        ("y_peers", ctypes.c_void_p * 8),
+        ("y_peers", ctypes.c_void_p * 8), ("y_multicast", ctypes.c_void_p),
     ]
 
 

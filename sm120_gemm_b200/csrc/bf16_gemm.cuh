@@ -56,6 +56,7 @@ struct YTarget {
     int num_peers = 0;
     long long ld = 0;               // row pitch of the destination matrices in elements
     int col_offset = 0;
+    void *multicast = nullptr;      // NVSwitch multicast address of the same matrix: one multimem store reaches every rank
 };
 
 struct GemmParams {
@@ -70,6 +71,8 @@ struct GemmParams {
     float alpha;          // epilogue scale (FP8 per-tensor: sx*sw)
     int y_targets;        // TMA-store epilogue: destination matrices (1, or the ranks of a sharded run)
     int y_col_offset;     // column of the destination where this GEMM's column 0 lands
+    bf16 *y_mc;           // non-null: multicast address of the destination (row pitch y_ld); multimem stores replace the TMA stores
+    long long y_ld;
     uint32_t *status;
     // block-scaled kinds: ue8m0 scale factors in 512-byte atoms of 128 rows x 4 K-blocks,
     // atom (row/128, kblock/4) at byte ((row/128) * sf_k_atoms + kblock/4) * 512
@@ -503,7 +506,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     if (j + EG >= BN / 64) release_acc();       // this group's last piece of the accumulator
                     fence_proxy_async_smem();
                     named_bar_sync(bar_a, 128);
-                    if (epi_tid == 0) {
+                    if (p.y_mc != nullptr) {
+                        // all-gather through NVSwitch: eight lanes read one staged 128-byte row piece and store it
+                        // once to the multicast address (16 rows per pass); the barrier at the top of the next
+                        // round keeps writers off this buffer until every reader is done
+                        const int piece = epi_tid & 7;
+                        const int ccol = n0 + j * 64 + piece * 8;
+#pragma unroll 2
+                        for (int r0 = 0; r0 < T::BM_CTA; r0 += 16) {
+                            const int r = r0 + (epi_tid >> 3);
+                            uint32_t a, b, c, d;
+                            ld_shared_v4(stg + r * 128 + ((piece ^ (r & 7)) << 4), a, b, c, d);
+                            if (m0 + r < p.M && ccol + 8 <= p.N)
+                                multimem_st_v4(p.y_mc + (size_t)(m0 + r) * p.y_ld + p.y_col_offset + ccol, a, b, c, d);
+                        }
+                    } else if (epi_tid == 0) {
                         for (int t = 0; t < p.y_targets; t++) tma_store_2d(&tmap_ys.m[t], stg, p.y_col_offset + n0 + j * 64, m0);
                         tma_store_commit();
                     }
@@ -802,7 +819,12 @@ struct UmmaGemmLauncher {
             if (rc != GEMM_OK) return rc;
         }
         int y_targets = 1;
-        if (fused_gather) {
+        if (fused_gather && yt->multicast) {
+            if (N % 8 != 0 || (reinterpret_cast<uintptr_t>(yt->multicast) & 15u))
+                return set_error(GEMM_ERR_ARG, "multicast stores need N %% 8 == 0 and a 16-byte aligned address");
+            y_targets = 0;
+            tys.m[0] = tx;
+        } else if (fused_gather) {
             // one map per rank's matrix; the extent stops at this block's last column so that a partial last
             // tile is clipped there and cannot spill into the next rank's columns
             y_targets = yt->num_peers;
@@ -834,6 +856,8 @@ struct UmmaGemmLauncher {
         p.status = dev->status;
         p.y_targets = y_targets;
         p.y_col_offset = fused_gather ? yt->col_offset : 0;
+        p.y_mc = fused_gather ? static_cast<bf16 *>(yt->multicast) : nullptr;
+        p.y_ld = fused_gather ? yt->ld : 0;
         p.sf_k_atoms = (K + 127) / 128;
         const long long work = (long long)p.num_m_blocks * p.num_n_blocks * (T::SPLIT_K > 0 ? T::SPLIT_K : p.num_k_blocks);
         int grid = 0;

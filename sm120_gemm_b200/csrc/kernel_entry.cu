@@ -80,6 +80,7 @@ int gemm_run_ex(const GemmArgs *a)
     sm100::YTarget yt;
     yt.peers = a->y_peers;
     yt.num_peers = a->y_num_peers;
+    yt.multicast = a->y_multicast;
     yt.ld = a->y_ld;
     yt.col_offset = a->y_col_offset;
     return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, static_cast<float *>(a->workspace), a->workspace_bytes, alpha,

@@ -9,6 +9,8 @@ module has no counterpart there.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 
 
@@ -46,7 +48,7 @@ class FusedNShardedGemm:
     tile and no interleave pass is needed.  ``run`` ends with a cross-rank barrier on the stream: after
     it, this rank's Y holds every rank's block.  Needs a TMA-store configuration (``e1``, no split-K)."""
 
-    def __init__(self, kernel, M: int, N: int, K: int, rank: int, world: int, group=None):
+    def __init__(self, kernel, M: int, N: int, K: int, rank: int, world: int, group=None, rotate: bool = True, peers=None, multicast: bool = True):
         import ctypes
 
         import torch
@@ -71,9 +73,21 @@ class FusedNShardedGemm:
         a = GemmArgs()
         a.M, a.N, a.K = M, self.plan.rows, K
         a.x_scale_f = a.w_scale_f = 1.0
-        a.y_num_peers, a.y_col_offset, a.y_ld = world, self.plan.row_start, N
-        for i, ptr in enumerate(ptrs):
-            a.y_peers[i] = ptr
+        # Destination order: own buffer first, then rank+1, rank+2, ... so that at any moment the ranks
+        # (which walk their tiles in step) send to eight different GPUs instead of all to the same one.
+        order = [(rank + i) % world if rotate else i for i in range(world)]
+        if peers is not None:       # subset of destinations (timing experiments: [rank] = no remote stores)
+            order = list(peers)
+        a.y_num_peers, a.y_col_offset, a.y_ld = len(order), self.plan.row_start, N
+        for i, r in enumerate(order):
+            a.y_peers[i] = ptrs[r]
+        # With an NVSwitch multicast mapping of the buffer one store reaches every rank, and each result byte
+        # leaves this GPU once instead of world-1 times; without one (or with fewer destinations than ranks)
+        # the epilogue stores to each peer in turn.
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.multicast = bool(multicast and mc and peers is None and self.plan.rows % 8 == 0
+                              and os.environ.get("SM100_GEMM_MULTICAST", "1") != "0")
+        a.y_multicast = mc if self.multicast else None
         self.args = a
 
     def run(self, X, W_shard):

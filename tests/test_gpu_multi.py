@@ -1,6 +1,7 @@
-"""N-sharded GEMM on 2 GPUs (skipped when fewer are visible): both gather paths -- epilogue TMA
-stores into every rank's Y, and NCCL all-gather + interleave -- must reproduce, bit for bit, the
-result of the same plugin run unsharded on one GPU, on every rank."""
+"""N-sharded GEMM on 2 GPUs (skipped when fewer are visible): every gather path -- epilogue TMA
+stores into each rank's Y, epilogue multimem stores to the NVSwitch multicast address of Y, and NCCL
+all-gather + interleave -- must reproduce, bit for bit, the result of the same plugin run unsharded
+on one GPU, on every rank."""
 import os
 import socket
 
@@ -20,13 +21,15 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, M, N, K, out_dir):
+def _worker(rank, world, port, M, N, K, out_dir, multicast):
     import torch.distributed as dist
 
     import sm120_gemm_b200 as g
     from sm120_gemm_b200.shard import FusedNShardedGemm, NShardedGemm, shard_plan
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TORCH_SYMM_MEM_DISABLE_MULTICAST="1", NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    if not multicast:
+        os.environ.update(TORCH_SYMM_MEM_DISABLE_MULTICAST="1", NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -39,7 +42,7 @@ def _worker(rank, world, port, M, N, K, out_dir):
     g.dispatch(k, M, N, K, X.data_ptr(), W.data_ptr(), Yref.data_ptr(), 0, st)     # unsharded, this GPU alone
     plan = shard_plan(N, world, rank)
     Wr = W[plan.row_start:plan.row_start + plan.rows].contiguous()
-    fused = FusedNShardedGemm(k, M, N, K, rank, world)
+    fused = FusedNShardedGemm(k, M, N, K, rank, world, multicast=multicast)
     fused.Y.fill_(float("nan"))
     dist.barrier()
     fused.run(X, Wr)
@@ -47,19 +50,25 @@ def _worker(rank, world, port, M, N, K, out_dir):
     NShardedGemm(k, M, N, K, rank, world).run(X, Wr, Yn)
     torch.cuda.synchronize()
     k.check_status()
-    ok = [bool(torch.equal(fused.Y, Yref)), bool(torch.equal(Yn, Yref))]
+    ok = [bool(torch.equal(fused.Y, Yref)), bool(torch.equal(Yn, Yref)), bool(fused.multicast)]
     np.save(os.path.join(out_dir, f"ok_{rank}.npy"), np.array(ok))
     dist.barrier()
     dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_sharded_equals_unsharded(tmp_path):
+@pytest.mark.parametrize("multicast", [False, True], ids=["peer_stores", "multicast_stores"])
+def test_two_gpu_sharded_equals_unsharded(tmp_path, multicast):
     import torch.multiprocessing as mp
 
-    world, M, N, K = 2, 1024, 2048, 1536
-    mp.spawn(_worker, args=(world, _free_port(), M, N, K, str(tmp_path)), nprocs=world, join=True)
+    world, M, N, K = 2, 1024 + 64, 2048, 1536       # M is not a tile multiple: the last row block is clipped
+    mp.spawn(_worker, args=(world, _free_port(), M, N, K, str(tmp_path), multicast), nprocs=world, join=True)
+    used = []
     for r in range(world):
         ok = np.load(tmp_path / f"ok_{r}.npy")
         assert ok[0], f"rank {r}: fused-epilogue result differs from the unsharded one"
         assert ok[1], f"rank {r}: NCCL all-gather result differs from the unsharded one"
+        used.append(bool(ok[2]))
+    if multicast and not all(used):
+        pytest.skip("no multicast mapping of symmetric memory on this node: the peer-store path ran instead")
+    assert all(used) == multicast
