@@ -65,6 +65,7 @@ struct GemmParams {
     int num_k_blocks;     // per split (stream-K: per tile)
     int group_n;          // width (in N tiles) of a rasterisation band
     int burst;            // k-blocks the producer requests together (1 .. STAGES)
+    int wait_sleep_ns;    // > 0: the epilogue's wait for an accumulator and the producer's wait for a free slot back off up to this long
     int l2_hint;          // 1: W loads evict-last, X loads evict-first (keeps a band of W panels in L2 while X streams)
     void *Y;              // bf16 output (direct epilogue)
     float *workspace;     // split-K partial sums [split][M][N]
@@ -144,8 +145,14 @@ __host__ __device__ __forceinline__ int streamk_owner(long long units, long long
     return (int)(((u + 1) * num_clusters - 1) / units);   // the c with range_begin(c) <= u < range_begin(c+1)
 }
 
-template <int OPK_, int BN_, int STAGES_, int CG_, int SPLIT_K_, int EPI_>
+// MB_ = 128-row blocks of X per CTA.  With MB_ = 2 a CTA owns 256 rows: every stage holds 32 KB of X and the
+// same B tile feeds two MMAs per K step, one per row block, each with its own accumulator.  Per flop that is a
+// quarter less operand traffic into shared memory (and out of L2) than MB_ = 1; the two 256-column accumulators
+// fill TMEM, so there is one accumulator stage and the two epilogue groups drain one row block each.
+template <int OPK_, int BN_, int STAGES_, int CG_, int SPLIT_K_, int EPI_, int MB_ = 1>
 struct UmmaGemmTraits {
+    static constexpr int MB = MB_;
+    static constexpr int EPI_ROWS = 128;                   // rows one epilogue group stages and stores at a time
     static constexpr int OPK = OPK_;
     static constexpr int BN = BN_;
     static constexpr int STAGES = STAGES_;
@@ -154,8 +161,9 @@ struct UmmaGemmTraits {
     static constexpr int EPI = (SPLIT_K_ > 1) ? EPI_DIRECT : EPI_;   // stream-K (0) keeps the chosen epilogue for whole tiles
     static constexpr int ELEM_BITS = (OPK_ == OPK_BF16) ? 16 : (OPK_ == OPK_MXFP4) ? 4 : 8;
     static constexpr bool BLOCK_SCALED = (OPK_ == OPK_MXFP8 || OPK_ == OPK_MXFP4);
-    static constexpr int BM_CTA = 128;                     // rows of X (and of the accumulator) per CTA
+    static constexpr int BM_CTA = 128 * MB_;               // rows of X per CTA (each accumulator covers 128 of them)
     static constexpr int BM = BM_CTA * CG_;                // rows of the tile
+    static constexpr int UMMA_M = 128 * CG_;               // M extent of one MMA instruction
     static constexpr int BK_BYTES = 128;                   // one swizzle span per row
     static constexpr int BK = BK_BYTES * 8 / ELEM_BITS;    // K elements per stage
     static constexpr int BK_COORD = (OPK_ == OPK_BF16) ? BK : BK_BYTES;   // the same, in tensor-map elements (bf16, else bytes)
@@ -171,7 +179,7 @@ struct UmmaGemmTraits {
     static constexpr int SF_BYTES = SF_A_BYTES + SF_B_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;   // bytes that arrive per stage
     static constexpr int OUT_CHUNK = 64;                   // output columns per TMA store (128 bytes of bf16)
-    static constexpr int STAGING_BYTES = (EPI == EPI_TMA) ? 2 * BM_CTA * OUT_CHUNK * 2 : 0;
+    static constexpr int STAGING_BYTES = (EPI == EPI_TMA) ? 2 * EPI_ROWS * OUT_CHUNK * 2 : 0;
     static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4;
     static constexpr int SF_RING_BYTES = (STAGES_ * SF_BYTES + 1023) / 1024 * 1024;   // keeps the staging tiles 1024-byte aligned
     static constexpr int SMEM_BYTES = STAGES_ * (A_BYTES + B_BYTES) + SF_RING_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + 16;
@@ -179,8 +187,9 @@ struct UmmaGemmTraits {
     static constexpr int ACC_STRIDE = (BN_ + 31) / 32 * 32;  // TMEM columns between the two accumulator buffers
     static constexpr int SF_COLS = SF_K_ATOMS * (1 + SF_N_ATOMS) * 4;   // TMEM columns of the staged scale factors
     // two FP32 accumulator buffers when they fit beside the scale factors, else one
-    static constexpr int ACC_STAGES = (2 * ACC_STRIDE + SF_COLS <= 512) ? 2 : 1;
-    static constexpr int ACC_COLS = ACC_STAGES * ACC_STRIDE + SF_COLS;
+    static constexpr int ACC_STAGE_COLS = MB_ * ACC_STRIDE;  // TMEM columns of one accumulator stage (MB_ row blocks side by side)
+    static constexpr int ACC_STAGES = (2 * ACC_STAGE_COLS + SF_COLS <= 512) ? 2 : 1;
+    static constexpr int ACC_COLS = ACC_STAGES * ACC_STAGE_COLS + SF_COLS;
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
     // Kernels with a single accumulator buffer cannot hide the epilogue behind the next main loop, so they
     // drain it with two epilogue groups of four warps (alternate 64- or 16-column pieces) instead of one.
@@ -190,6 +199,8 @@ struct UmmaGemmTraits {
     static_assert(EPI != EPI_TMA || BN_ % 64 == 0, "the TMA-store epilogue writes 64-column boxes");
     static_assert((BN_ / CG_) % 8 == 0, "each CTA loads whole 8-row swizzle groups of W");
     static_assert(CG_ == 1 || CG_ == 2, "CTA group is 1 or 2");
+    static_assert(MB_ == 1 || (MB_ == 2 && SPLIT_K_ == 1 && EPI_ == EPI_TMA && !BLOCK_SCALED && ACC_STAGES == 1),
+                  "two row blocks per CTA: whole-K tiles, TMA-store epilogue, dense operand kinds, one accumulator stage");
     static_assert(STAGES_ >= 2, "at least two ring stages");
     static_assert(!BLOCK_SCALED || BN_ % 128 == 0, "block-scaled tiles: BN a multiple of the 128-row scale atom");
     static_assert(ACC_COLS <= 512, "TMEM has 512 columns");
@@ -287,6 +298,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             const uint32_t full_leader = (CG == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
             const uint64_t pol_w = l2_policy_evict_last(), pol_x = l2_policy_evict_first();
             bool ok = true;
+#ifdef SM100_DEBUG_NOLOAD
+            int debug_loads = 0;
+#endif
             WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
             WorkItem w;
             while (ok && sched.next(w)) {
@@ -304,7 +318,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     int st = stage;
                     uint32_t ph = phase;
                     for (int d = 0; d < nb_burst; d++) {
-                        if (!mbar_wait(empty_bar(st), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, st)) {
+                        if (!mbar_wait(empty_bar(st), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, st, p.wait_sleep_ns > 128 ? 128 : p.wait_sleep_ns)) {
                             ok = false;
                             break;
                         }
@@ -313,6 +327,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     if (!ok) break;
                     for (int d = 0; d < nb_burst; d++) {
                         const int kx = (kb0 + kb + d) * T::BK_COORD;
+#ifdef SM100_DEBUG_NOLOAD
+                        // measurement aid (results are meaningless): after the ring's first fill no operand is
+                        // loaded any more and the stages are handed over as they are, which shows what the
+                        // MMA side sustains with no load traffic into shared memory
+                        if (debug_loads >= STAGES) {
+                            if (cta_rank == 0) mbar_arrive(full_bar(stage));
+                            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                            continue;
+                        }
+                        debug_loads++;
+#endif
                         if constexpr (CG == 1) {
                             mbar_arrive_expect_tx(full_bar(stage), T::STAGE_BYTES);
                             if (p.l2_hint) {
@@ -343,10 +368,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (cta_rank == 0) {   // every lane runs the loop; one elected lane issues (see elect_one_sync)
-            const uint32_t instr = (T::OPK == OPK_BF16) ? make_idesc(UMMA_BF16, UMMA_BF16, T::BM, BN)
-                                                         : make_idesc(UMMA_E4M3, UMMA_E4M3, T::BM, BN);
+            const uint32_t instr = (T::OPK == OPK_BF16) ? make_idesc(UMMA_BF16, UMMA_BF16, T::UMMA_M, BN)
+                                                         : make_idesc(UMMA_E4M3, UMMA_E4M3, T::UMMA_M, BN);
             // scale factors live behind the accumulator buffers: X atoms, then W atoms
-            const uint32_t sfa_tmem = tmem_base + (uint32_t)(T::ACC_STAGES * T::ACC_STRIDE);
+            const uint32_t sfa_tmem = tmem_base + (uint32_t)(T::ACC_STAGES * T::ACC_STAGE_COLS);
             const uint32_t sfb_tmem = sfa_tmem + (uint32_t)(T::SF_K_ATOMS * 4);
             int stage = 0;
             uint32_t phase = 0;
@@ -359,7 +384,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 const uint32_t acc_phase = (titer / T::ACC_STAGES) & 1;
                 if (!__all_sync(0xffffffffu, mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, acc))) break;
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * T::ACC_STRIDE);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * T::ACC_STAGE_COLS);
                 for (int kb = 0; kb < w.kb_count; kb++) {
                     if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage))) {
                         ok = false;
@@ -386,17 +411,24 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         if constexpr (T::OPK == OPK_MXFP8) {
                             // 4 instructions of 32 K-elements share one atom: instruction k uses scale byte k
                             umma_mxf8<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k),
-                                      make_idesc_block_scaled(UMMA_E4M3, UMMA_E4M3, T::BM, BN, k, k), sfa_tmem, sfb_tmem, accumulate);
+                                      make_idesc_block_scaled(UMMA_E4M3, UMMA_E4M3, T::UMMA_M, BN, k, k), sfa_tmem, sfb_tmem, accumulate);
                         } else if constexpr (T::OPK == OPK_MXFP4) {
                             // 4 instructions of 64 K-elements: two per atom, each using one half (2 scale bytes)
                             umma_mxf4<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k),
-                                      make_idesc_block_scaled(UMMA_MXF4_E2M1, UMMA_MXF4_E2M1, T::BM, BN, (k & 1) * 2, (k & 1) * 2),
+                                      make_idesc_block_scaled(UMMA_MXF4_E2M1, UMMA_MXF4_E2M1, T::UMMA_M, BN, (k & 1) * 2, (k & 1) * 2),
                                       sfa_tmem + (k >> 1) * 4, sfb_tmem + (k >> 1) * (T::SF_N_ATOMS * 4), accumulate);
                         } else
-                        if constexpr (T::OPK == OPK_BF16)
-                            umma_f16<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, accumulate);
-                        else
-                            umma_f8f6f4<CG>(d_tmem, advance_desc_k(a_desc, k), advance_desc_k(b_desc, k), instr, accumulate);
+                        if constexpr (T::OPK == OPK_BF16) {
+#pragma unroll
+                            for (int blk = 0; blk < T::MB; blk++)   // row block blk: X rows 128*blk.. of this CTA, 16 KB further on
+                                umma_f16<CG>(d_tmem + (uint32_t)(blk * T::ACC_STRIDE), advance_desc_k(a_desc + (uint64_t)(blk * 1024), k),
+                                             advance_desc_k(b_desc, k), instr, accumulate);
+                        } else {
+#pragma unroll
+                            for (int blk = 0; blk < T::MB; blk++)
+                                umma_f8f6f4<CG>(d_tmem + (uint32_t)(blk * T::ACC_STRIDE), advance_desc_k(a_desc + (uint64_t)(blk * 1024), k),
+                                                advance_desc_k(b_desc, k), instr, accumulate);
+                        }
                     }
                     if constexpr (CG == 1) umma_commit(empty_bar(stage)); else umma_commit_pair(empty_bar(stage), 3);
                     }
@@ -426,16 +458,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         for (; sched.next(w); titer++) {
             int mb, nb;
             tile_to_mn(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
-            const int m0 = mb * T::BM + (int)cta_rank * T::BM_CTA;
+            // two row blocks per CTA: epilogue group eg drains the accumulator of row block eg
+            const int blk = (T::MB == 2) ? eg : 0;
+            const int m0 = mb * T::BM + (int)cta_rank * T::BM_CTA + blk * 128;
             const int n0 = nb * BN;
             const int acc = titer % T::ACC_STAGES;
             const uint32_t acc_phase = (titer / T::ACC_STAGES) & 1;
             // all 128 epilogue threads must take the same decision, or the ones that go on would
             // wait at a named barrier for the ones that left
-            const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, acc);
+            const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, acc, p.wait_sleep_ns);
             if (!named_bar_and(bar_b, 128, got)) break;
             tc_fence_after_sync();
-            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * T::ACC_STRIDE);
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * T::ACC_STAGE_COLS + blk * T::ACC_STRIDE);
             const int grow = m0 + row_in_tile;
             // hands the drained accumulator buffer back to the MMA issuer
             auto release_acc = [&]() {
@@ -479,12 +513,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             } else if constexpr (T::EPI == EPI_TMA) {
                 // bf16 through swizzled shared memory and TMA stores of 128 x 64 boxes
 #pragma unroll 1
-                for (int j = eg; j < BN / 64; j += EG) {
+                constexpr int J_STEP = (T::MB == 2) ? 1 : EG;     // pieces alternate between the groups unless each has its own row block
+                for (int j = (T::MB == 2) ? 0 : eg; j < BN / 64; j += J_STEP) {
                     // the store that last read this staging buffer must have finished reading it (one group:
                     // two buffers in turn; two groups: one buffer each)
                     if (epi_tid == 0) { if constexpr (EG == 1) tma_store_wait_read<1>(); else tma_store_wait_read<0>(); }
                     named_bar_sync(bar_a, 128);
-                    const uint32_t stg = stg_base + (EG == 1 ? buf : eg) * (T::BM_CTA * 128);
+                    const uint32_t stg = stg_base + (EG == 1 ? buf : eg) * (T::EPI_ROWS * 128);
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         uint32_t r[32];
@@ -503,7 +538,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                             st_shared_v4(stg + row_in_tile * 128 + chunk * 16, pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
                         }
                     }
-                    if (j + EG >= BN / 64) release_acc();       // this group's last piece of the accumulator
+                    if (j + J_STEP >= BN / 64) release_acc();       // this group's last piece of the accumulator
                     fence_proxy_async_smem();
                     named_bar_sync(bar_a, 128);
                     if (p.y_mc != nullptr) {
@@ -513,7 +548,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         const int piece = epi_tid & 7;
                         const int ccol = n0 + j * 64 + piece * 8;
 #pragma unroll 2
-                        for (int r0 = 0; r0 < T::BM_CTA; r0 += 16) {
+                        for (int r0 = 0; r0 < T::EPI_ROWS; r0 += 16) {
                             const int r = r0 + (epi_tid >> 3);
                             uint32_t a, b, c, d;
                             ld_shared_v4(stg + r * 128 + ((piece ^ (r & 7)) << 4), a, b, c, d);
@@ -670,6 +705,19 @@ inline cudaLaunchConfig_t dependent_launch_config(unsigned blocks, unsigned thre
 }
 
 // L2 cache hints on the operand loads.  SM100_GEMM_L2HINT=0/1 overrides (tuning runs).
+// Back-off cap of the long waits, in ns: SM100_GEMM_WAIT_SLEEP overrides (0 = poll back to back); by
+// default 4 ns per k-block of a tile, at most 1024, so short tiles keep their latency.
+inline int wait_sleep_ns(int num_k_blocks)
+{
+    static const int env = []() {
+        const char *e = getenv("SM100_GEMM_WAIT_SLEEP");
+        return e ? atoi(e) : -1;
+    }();
+    if (env >= 0) return env;
+    const int v = num_k_blocks * 4;
+    return v > 1024 ? 1024 : v;
+}
+
 inline int l2_hint_mode(int M, int N, int K)
 {
     static const int override_h = []() {
@@ -831,11 +879,11 @@ struct UmmaGemmLauncher {
             for (int t = 0; t < y_targets; t++) {
                 if (!yt->peers[t]) return set_error(GEMM_ERR_ARG, "null peer pointer %d", t);
                 rc = make_tmap_2d(&tys.m[t], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, yt->peers[t], (uint64_t)(yt->col_offset + N), (uint64_t)M,
-                                  (uint64_t)yt->ld * 2, T::OUT_CHUNK, T::BM_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
+                                  (uint64_t)yt->ld * 2, T::OUT_CHUNK, T::EPI_ROWS, CU_TENSOR_MAP_SWIZZLE_128B);
                 if (rc != GEMM_OK) return rc;
             }
         } else if (T::EPI == EPI_TMA) {
-            rc = make_tmap_2d(&tys.m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, Y, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, T::OUT_CHUNK, T::BM_CTA,
+            rc = make_tmap_2d(&tys.m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, Y, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, T::OUT_CHUNK, T::EPI_ROWS,
                               CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc != GEMM_OK) return rc;
         } else {
@@ -850,6 +898,7 @@ struct UmmaGemmLauncher {
         p.group_n = band_width(T::BN);
         p.burst = load_burst(T::STAGES);
         p.l2_hint = l2_hint_mode(M, N, K);
+        p.wait_sleep_ns = wait_sleep_ns(p.num_k_blocks);
         p.Y = Y;
         p.workspace = workspace;
         p.alpha = alpha;

@@ -4,7 +4,7 @@
 // Same role as the reference's src/kernel_entry.cu.in:5-27 (a CMake-configured template with
 // eight @VAR@ constants and one exported gemm_run); here the build passes
 //   -DGEMM_DT=<0..4> -DGEMM_BN=<64|128|192|256> -DGEMM_STAGES=<n> -DGEMM_CG=<1|2>
-//   -DGEMM_SK=<split-K> -DGEMM_AB=<0|1 operand swap> -DGEMM_EPI=<0|1>
+//   -DGEMM_SK=<split-K> -DGEMM_AB=<0|1 operand swap> -DGEMM_EPI=<0|1> -DGEMM_MB=<1|2 row blocks per CTA>
 #include "bf16_gemm.cuh"
 #include "w4a16_gemm.cuh"
 
@@ -21,7 +21,11 @@ constexpr int CG = GEMM_CG;
 constexpr int SK = GEMM_SK;
 constexpr int AB = GEMM_AB;
 constexpr int EPI = GEMM_EPI;
-constexpr int BM = 128 * CG;
+#ifndef GEMM_MB
+#define GEMM_MB 1
+#endif
+constexpr int MB = GEMM_MB;          // 128-row blocks of X per CTA
+constexpr int BM = 128 * CG * MB;
 
 #if GEMM_DT == 3
 // W4A16: operands swapped (AB = 1), BN is M padded, work is always cut stream-K fashion (SK = 0)
@@ -31,7 +35,7 @@ using Launcher = sm100::W4A16Launcher<Traits>;
 #else
 static_assert(AB == 0, "operand swap is not part of this kernel");
 constexpr int OPK = DT == GEMM_DT_BF16 ? sm100::OPK_BF16 : DT == GEMM_DT_FP8 ? sm100::OPK_E4M3 : DT == GEMM_DT_MXFP8 ? sm100::OPK_MXFP8 : sm100::OPK_MXFP4;
-using Traits = sm100::UmmaGemmTraits<OPK, BN, STAGES, CG, SK, EPI>;
+using Traits = sm100::UmmaGemmTraits<OPK, BN, STAGES, CG, SK, EPI, MB>;
 using Launcher = sm100::UmmaGemmLauncher<Traits>;
 #endif
 

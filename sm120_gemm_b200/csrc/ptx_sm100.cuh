@@ -140,15 +140,23 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait.  Returns false when the CTA is aborting (this waiter or another one gave
 // up); `abort_flag` is a word in shared memory, `status` the global status block
 // (status[0] = code, [1] = blockIdx.x, [2] = detail) or nullptr.
+// `sleep_cap_ns` > 0 makes a long wait cheap: between polls the thread sleeps 32 ns, then twice as long
+// each time up to the cap, instead of polling back to back (warps that wait for most of a tile's main
+// loop otherwise spend issue slots and power on the poll).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t *status, uint32_t code, uint32_t detail)
+                                          uint32_t *status, uint32_t code, uint32_t detail, uint32_t sleep_cap_ns = 0)
 {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = 0;
     uint32_t spins = 0;
+    uint32_t ns = 32;
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 0xffu) == 0) {
+        if (sleep_cap_ns) {
+            __nanosleep(ns);
+            if (ns < sleep_cap_ns) ns <<= 1;
+        }
+        if ((++spins & (sleep_cap_ns ? 0xfu : 0xffu)) == 0) {
             if (*abort_flag) return false;
             const long long now = clock64();
             if (t0 == 0) t0 = now;

@@ -5,7 +5,8 @@ BM,BN in {64,128} x stages x consumer warpgroups x warp tilings x split-K under 
 shared-memory cap for the mma.sync kernel), re-derived for the tcgen05 design:
 
   dt       bf16 | fp8 | mxfp8 | w4a16 | w4a4
-  bm       128 (one CTA) or 256 (CTA pair, cta_group::2); always 128*cg
+  bm       rows of X per tile = 128 * cg * (row blocks per CTA): 128 (one CTA), 256 (CTA pair, cta_group::2),
+           512 (CTA pair with two 128-row blocks per CTA: one B tile feeds two MMAs)
   bn       multiple of 16 up to 256  (UMMA N; two FP32 accumulator buffers need 2*bn <= 512 TMEM columns;
            the TMA-store epilogue needs a multiple of 64)
   bk       one 128-byte swizzle span of K per stage: 64 bf16, 128 fp8, 256 fp4 elements
@@ -48,6 +49,11 @@ class GemmConfig:
     swap_ab: int
     epi: int
 
+    @property
+    def mb(self) -> int:
+        """128-row blocks of X per CTA."""
+        return max(1, self.bm // (128 * self.cg))
+
     def name(self) -> str:
         return (f"{self.dt}_bm{self.bm}_bn{self.bn}_bk{self.bk}_s{self.num_stages}_cg{self.cg}"
                 f"_sk{self.split_k}_ab{self.swap_ab}_e{self.epi}")
@@ -67,7 +73,7 @@ class GemmConfig:
             load_stages = min(4, (224 * 1024 - self.num_stages * 2 * 128 * 128) // load_stage)
             return (self.num_stages * 2 * 128 * 128 + load_stages * load_stage
                     + (2 * load_stages + 3 * self.num_stages) * 8 + 16 + 1024)
-        a = 128 * 128
+        a = 128 * 128 * self.mb
         b = (self.bn // self.cg) * 128
         # block-scaled kinds stage one 512-byte scale atom per 128 rows and 128 K-elements
         k_atoms = self.bk // 128 if self.dt in ("mxfp8", "w4a4") else 0
@@ -96,7 +102,7 @@ class GemmConfig:
     def defines(self) -> list[str]:
         return [f"-DGEMM_DT={DT_IDS[self.dt]}", f"-DGEMM_BN={self.bn}", f"-DGEMM_STAGES={self.num_stages}",
                 f"-DGEMM_CG={self.cg}", f"-DGEMM_SK={self.split_k}", f"-DGEMM_AB={self.swap_ab}",
-                f"-DGEMM_EPI={self.epi}", f"-DGEMM_NAME={self.name()}"]
+                f"-DGEMM_EPI={self.epi}", f"-DGEMM_MB={self.mb}", f"-DGEMM_NAME={self.name()}"]
 
 
 def max_stages(dt: str, bn: int, cg: int, sk: int, epi: int, cap: int = MAX_SMEM) -> int:
@@ -155,6 +161,11 @@ def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8", "mxfp8", "w4a
                     for s in stage_opts:
                         if s >= 2:
                             out.append(GemmConfig(dt, 128 * cg, bn, bk, s, cg, 1, 0, epi))
+        # two row blocks per CTA (512 x 256 tiles on a CTA pair): a quarter less operand traffic per flop, for large shapes
+        for s in (4, 3):
+            c = GemmConfig(dt, 512, 256, bk, s, 2, 1, 0, 1)
+            if c.smem_bytes() <= max_smem:
+                out.append(c)
         # split-K: for shapes with too few output tiles to fill 148 SMs (decode, M <= 128)
         for cg, bn in ((1, 64), (1, 128), (1, 256), (2, 128), (2, 256)):
             for sk in (2, 4, 7, 8, 16):

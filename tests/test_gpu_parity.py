@@ -66,7 +66,8 @@ EDGE_SHAPES = [(1, 8, 8), (1, 64, 64), (16, 256, 512), (127, 264, 72), (129, 8, 
 
 @pytest.mark.parametrize("name", [BEST, "bf16_bm128_bn128_bk64_s6_cg1_sk1_ab0_e1", "bf16_bm128_bn128_bk64_s7_cg1_sk1_ab0_e0",
                                   "bf16_bm256_bn192_bk64_s6_cg2_sk1_ab0_e1", "bf16_bm256_bn256_bk64_s7_cg2_sk1_ab0_e0",
-                                  "bf16_bm128_bn256_bk64_s4_cg1_sk0_ab0_e0", "bf16_bm256_bn256_bk64_s7_cg2_sk0_ab0_e0"])
+                                  "bf16_bm128_bn256_bk64_s4_cg1_sk0_ab0_e0", "bf16_bm256_bn256_bk64_s7_cg2_sk0_ab0_e0",
+                                  "bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1"])
 def test_ragged_and_tiny_shapes(registry, cuda_device, name):
     """M, N, K that are not multiples of the tile (the reference rejects these,
     src/gemm_config.h:34-38): partial tiles, a single k-block, exactly / one more than the ring depth."""
@@ -75,6 +76,18 @@ def test_ragged_and_tiny_shapes(registry, cuda_device, name):
     for (M, N, K) in EDGE_SHAPES:
         X, W = o.make_inputs(M, N, K, seed=M + N + K)
         dense_ok(to_bits(run_bf16(k, to_dev(X), to_dev(W))), o.gemm_bf16(X, W), X, W, K)
+
+
+def test_two_row_blocks_per_cta_bit_identical(registry, cuda_device):
+    """The 512 x 256 tile (two 128-row blocks per CTA sharing each B tile) adds the same products in the same
+    order as the 256 x 256 tile, so the two plugins must agree bit for bit, partial last tiles included."""
+    tall, base = registry.find("bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1"), registry.find("bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1")
+    assert tall is not None and base is not None
+    for (M, N, K) in [(2048, 1024, 2048), (1000, 520, 1088), (513, 264, 64), (4096 + 384, 2048 + 8, 4096)]:
+        X, W = o.make_inputs(M, N, K, seed=7 * M + N + K)
+        Xd, Wd = to_dev(X), to_dev(W)
+        a, b = to_bits(run_bf16(tall, Xd, Wd)), to_bits(run_bf16(base, Xd, Wd))
+        assert np.array_equal(a, b), f"{M}x{N}x{K}: {np.count_nonzero(a != b)} elements differ"
 
 
 def test_one_hot_probe(registry, cuda_device):
