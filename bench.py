@@ -26,10 +26,13 @@ sys.path.insert(0, ROOT)
 
 M = N = K = 16384
 WORKLOAD = "bf16 gemm Y=X*W^T M=N=K=16384, X,W~N(0,1) seed 2, fp32 accumulate, bf16 out (BASELINE config 3)"
-DEFAULT_KERNEL = "bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1"
+DEFAULT_KERNELS = ["bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1", "bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1"]
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel at this workload,
 # from the ncu capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES = 13662148608 + 537297664   # profiles/kernel_families_limited_metrics.md, 16384^3 row
+NCU_TRAFFIC_BYTES = {   # profiles/kernel_families_limited_metrics.md, 16384^3 rows
+    "bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1": 12197871872 + 531051008,
+    "bf16_bm256_bn256_bk64_s4_cg2_sk1_ab0_e1": 13662148608 + 537297664,
+}
 
 
 def load_peaks():
@@ -170,12 +173,14 @@ def main():
     names = [args.kernel] if args.kernel else []
     if not names:
         hit = cache.lookup(M, N // world, K, "bf16", 1)
-        names = ([hit[0].name()] if hit else []) + [DEFAULT_KERNEL]
+        names = ([hit[0].name()] if hit else []) + DEFAULT_KERNELS
     cands = []
     for n in dict.fromkeys(names):
         k = reg.find(n)
         if k is None:
             sys.exit(f"plugin {n} is not built")
+        if world > 1 and args.gather == "fused" and not args.kernel and (k.config.epi != 1 or k.config.split_k != 1):
+            continue        # the fused gather needs a TMA-store epilogue
         cands.append(k)
 
     plan_rows = N // world
@@ -310,7 +315,7 @@ def main():
         kflops = flops / world
         achieved = kflops / (launch_ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "achieved": achieved if world == 1 else None, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["bf16_tflops"] if world == 1 else None, "traffic": NCU_TRAFFIC_BYTES,
+                    "frac": achieved / peaks["bf16_tflops"] if world == 1 else None, "traffic": NCU_TRAFFIC_BYTES.get(kern.config.name()) if world == 1 else None,
                     "peak_source": f"{peaks['source']} (cuBLAS bf16 burst; sustained {peaks['bf16_tflops_sustained']})",
                     "kernel": f"umma_gemm_kernel<{kern.config.name()}>", "flops_per_launch": kflops, "avg_launch_ms": launch_ms}
         out = {

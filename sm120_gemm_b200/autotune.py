@@ -120,6 +120,7 @@ def main():
     ap.add_argument("--force", action="store_true", help="re-tune shapes already in the cache")
     ap.add_argument("--quiet", action="store_true")
     ap.add_argument("--json", default=None, help="also write per-shape results to this file")
+    ap.add_argument("--match", default=None, help="only try plugins whose name matches this regular expression")
     args = ap.parse_args()
     import torch
 
@@ -144,7 +145,12 @@ def main():
         if hit and not args.force:
             print(f"  cached: {hit[0].name()}  {hit[1]:.4f} ms")
             continue
-        best, ms, cublas_ms, results = tune_shape(reg, M, N, K, verbose=not args.quiet)
+        only = None
+        if args.match:
+            import re
+
+            only = {k.config.name() for k in reg.kernels if re.search(args.match, k.config.name())}
+        best, ms, cublas_ms, results = tune_shape(reg, M, N, K, verbose=not args.quiet, only=only)
         if best is None:
             print("  NO VALID CONFIG")
             continue

@@ -743,13 +743,14 @@ inline int load_burst(int stages)
 
 // Width of a rasterisation band in tiles.  SM100_GEMM_GROUP_N overrides the built-in choice
 // (read once; meant for tuning runs).
-inline int band_width(int bn)
+inline int band_width(int bn, int mb = 1)
 {
     static const int override_n = []() {
         const char *e = std::getenv("SM100_GEMM_GROUP_N");
         return e ? std::atoi(e) : 0;
     }();
     if (override_n > 0) return override_n;
+    if (mb == 2) return 16;      // 512-row tiles: a band of 16 x 256 columns keeps a wave about square
     return bn >= 256 ? 8 : 16;
 }
 
@@ -895,10 +896,11 @@ struct UmmaGemmLauncher {
         p.num_m_blocks = (M + T::BM - 1) / T::BM;
         p.num_n_blocks = (N + T::BN - 1) / T::BN;
         p.num_k_blocks = ((K + T::BK - 1) / T::BK) / (T::SPLIT_K > 0 ? T::SPLIT_K : 1);
-        p.group_n = band_width(T::BN);
+        p.group_n = band_width(T::BN, T::MB);
         p.burst = load_burst(T::STAGES);
         p.l2_hint = l2_hint_mode(M, N, K);
-        p.wait_sleep_ns = wait_sleep_ns(p.num_k_blocks);
+        // with a single accumulator stage the epilogue's wake-up is on the critical path of every tile
+        p.wait_sleep_ns = wait_sleep_ns(T::ACC_STAGES == 1 ? (p.num_k_blocks < 16 ? p.num_k_blocks : 16) : p.num_k_blocks);
         p.Y = Y;
         p.workspace = workspace;
         p.alpha = alpha;
