@@ -778,7 +778,11 @@ struct UmmaGemmLauncher {
 
     // persistent grid: as many CTAs (CTA pairs) as can be resident at once, capped by the
     // tile count and by `sm_limit`
-    static int grid_size(const DeviceInfo &dev, int total_tiles, int sm_limit, int *out)
+    // `balance`: with a fixed work list, shrink the grid to ceil(work / waves) units, the smallest grid that
+    // still finishes in the same number of waves.  Nothing waits for a half-empty last wave then, and at the
+    // power cap the SMs left out pay for a higher clock on the ones that work (256 tiles on 74 CTA pairs take
+    // four rounds either way; on 64 pairs no pair idles during the fourth).
+    static int grid_size(const DeviceInfo &dev, int total_tiles, int sm_limit, int *out, bool balance = false)
     {
         static int max_clusters[MAX_DEVICES] = {0};
         int devid = 0;
@@ -809,6 +813,10 @@ struct UmmaGemmLauncher {
         int units = sms / T::CG;
         if (units < 1) units = 1;
         if (units > total_tiles) units = total_tiles;
+        if (balance && T::SPLIT_K >= 1) {
+            const int waves = (total_tiles + units - 1) / units;
+            units = (total_tiles + waves - 1) / waves;
+        }
         *out = units * T::CG;
         return GEMM_OK;
     }
@@ -912,7 +920,9 @@ struct UmmaGemmLauncher {
         p.sf_k_atoms = (K + 127) / 128;
         const long long work = (long long)p.num_m_blocks * p.num_n_blocks * (T::SPLIT_K > 0 ? T::SPLIT_K : p.num_k_blocks);
         int grid = 0;
-        rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &grid);
+        // compute-bound shapes only: a memory-bound one (M <= 128 rows) wants every SM's loads in flight
+        static const bool balance_on = []() { const char *e = std::getenv("SM100_GEMM_BALANCE"); return !e || std::atoi(e) != 0; }();
+        rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &grid, balance_on && M >= 512);
         if (rc != GEMM_OK) return rc;
         if (T::SPLIT_K == 0 && grid > STREAMK_MAX_CTAS) grid = STREAMK_MAX_CTAS - STREAMK_MAX_CTAS % T::CG;
 
