@@ -179,7 +179,10 @@ struct UmmaGemmTraits {
     static constexpr int SF_BYTES = SF_A_BYTES + SF_B_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;   // bytes that arrive per stage
     static constexpr int OUT_CHUNK = 64;                   // output columns per TMA store (128 bytes of bf16)
-    static constexpr int STAGING_BYTES = (EPI == EPI_TMA) ? 2 * EPI_ROWS * OUT_CHUNK * 2 : 0;
+    // staging buffers of 128 rows x 64 bf16: two (one epilogue group: used in turn; two groups: one each), or
+    // four when two row blocks per CTA leave room (three ring stages): each group then has two in turn
+    static constexpr int STAGING_BUFS = (MB_ == 2 && STAGES_ <= 3) ? 4 : 2;
+    static constexpr int STAGING_BYTES = (EPI == EPI_TMA) ? STAGING_BUFS * EPI_ROWS * OUT_CHUNK * 2 : 0;
     static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4;
     static constexpr int SF_RING_BYTES = (STAGES_ * SF_BYTES + 1023) / 1024 * 1024;   // keeps the staging tiles 1024-byte aligned
     static constexpr int SMEM_BYTES = STAGES_ * (A_BYTES + B_BYTES) + SF_RING_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + 16;
@@ -512,14 +515,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 release_acc();
             } else if constexpr (T::EPI == EPI_TMA) {
                 // bf16 through swizzled shared memory and TMA stores of 128 x 64 boxes
-#pragma unroll 1
                 constexpr int J_STEP = (T::MB == 2) ? 1 : EG;     // pieces alternate between the groups unless each has its own row block
+#pragma unroll 1
                 for (int j = (T::MB == 2) ? 0 : eg; j < BN / 64; j += J_STEP) {
-                    // the store that last read this staging buffer must have finished reading it (one group:
-                    // two buffers in turn; two groups: one buffer each)
-                    if (epi_tid == 0) { if constexpr (EG == 1) tma_store_wait_read<1>(); else tma_store_wait_read<0>(); }
+                    // the store that last read this staging buffer must have finished reading it (a group owns one
+                    // buffer, or two that it uses in turn)
+                    constexpr int NBUF = T::STAGING_BUFS / EG;      // buffers this group owns
+                    if (epi_tid == 0) tma_store_wait_read<NBUF - 1>();
                     named_bar_sync(bar_a, 128);
-                    const uint32_t stg = stg_base + (EG == 1 ? buf : eg) * (T::EPI_ROWS * 128);
+                    const uint32_t stg = stg_base + (eg * NBUF + (NBUF == 2 ? buf : 0)) * (T::EPI_ROWS * 128);
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         uint32_t r[32];

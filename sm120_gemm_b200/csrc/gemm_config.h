@@ -92,7 +92,7 @@ struct GemmConfig {
         const size_t k_atoms = (dt == GEMM_DT_MXFP8 || dt == GEMM_DT_W4A4) ? bk / 128 : 0;   // 512-byte scale atoms per stage
         const size_t sf_ring = (num_stages * k_atoms * (1 + (bn + 127) / 128) * 512 + 1023) / 1024 * 1024;
         const size_t a = (size_t)128 * 128 * (bm / (128 * cg) > 0 ? bm / (128 * cg) : 1), b = (size_t)(bn / cg) * 128;
-        const size_t staging = (split_k <= 1 && epi == 1) ? 2 * 128 * 64 * 2 : 0;
+        const size_t staging = (split_k <= 1 && epi == 1) ? (size_t)((bm / (128 * cg) == 2 && num_stages <= 3) ? 4 : 2) * 128 * 64 * 2 : 0;
         const size_t barriers = (2 * (size_t)num_stages + 4) * 8 + 16;
         return num_stages * (a + b) + sf_ring + staging + barriers + 1024;
     }

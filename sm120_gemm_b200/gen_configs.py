@@ -79,7 +79,7 @@ class GemmConfig:
         k_atoms = self.bk // 128 if self.dt in ("mxfp8", "w4a4") else 0
         sf = k_atoms * (1 + -(-self.bn // 128)) * 512
         epi = 0 if self.split_k > 1 else self.epi
-        staging = 2 * 128 * 64 * 2 if epi == 1 else 0
+        staging = (4 if self.mb == 2 and self.num_stages <= 3 else 2) * 128 * 64 * 2 if epi == 1 else 0
         barriers = (2 * self.num_stages + 4) * 8 + 16
         sf_ring = -(-self.num_stages * sf // 1024) * 1024
         return self.num_stages * (a + b) + sf_ring + staging + barriers + 1024

@@ -26,7 +26,7 @@ def test_config_name_roundtrip_all_generated():
     assert len(cfgs) == len({c.name() for c in cfgs}) > 40
     for c in cfgs:
         assert g.GemmConfig.parse(c.name()) == c
-        assert c.bm == 128 * c.cg and c.smem_bytes() <= 232448
+        assert c.bm in (128 * c.cg, 256 * c.cg) and c.mb == c.bm // (128 * c.cg) and c.smem_bytes() <= 232448
     assert g.GemmConfig.parse("bm128_bn64_bk64_s3_cwg2_wm32_wn32_sk1") is None
     assert g.GemmConfig.parse("bf16_bm128_bn128_bk64_s4_cg1_sk1_ab0_e1x") is None
 
