@@ -10,7 +10,7 @@ import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
-KERNEL = "bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1"
+KERNELS = ["bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1", "bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1"]
 
 
 def _free_port():
@@ -21,7 +21,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, M, N, K, out_dir, multicast):
+def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel):
     import torch.distributed as dist
 
     import sm120_gemm_b200 as g
@@ -33,7 +33,7 @@ def _worker(rank, world, port, M, N, K, out_dir, multicast):
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    k = g.load_plugin(os.path.join(g.KERNEL_DIR, f"libgemm_{KERNEL}.so"))
+    k = g.load_plugin(os.path.join(g.KERNEL_DIR, f"libgemm_{kernel}.so"))
     gen = torch.Generator(device=dev); gen.manual_seed(7)          # same stream on every rank
     X = torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16)
     W = torch.randn((N, K), device=dev, generator=gen).to(torch.bfloat16)
@@ -57,12 +57,13 @@ def _worker(rank, world, port, M, N, K, out_dir, multicast):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("kernel", KERNELS, ids=["tile256x256", "tile512x256"])
 @pytest.mark.parametrize("multicast", [False, True], ids=["peer_stores", "multicast_stores"])
-def test_two_gpu_sharded_equals_unsharded(tmp_path, multicast):
+def test_two_gpu_sharded_equals_unsharded(tmp_path, multicast, kernel):
     import torch.multiprocessing as mp
 
     world, M, N, K = 2, 1024 + 64, 2048, 1536       # M is not a tile multiple: the last row block is clipped
-    mp.spawn(_worker, args=(world, _free_port(), M, N, K, str(tmp_path), multicast), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), M, N, K, str(tmp_path), multicast, kernel), nprocs=world, join=True)
     used = []
     for r in range(world):
         ok = np.load(tmp_path / f"ok_{r}.npy")
