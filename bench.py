@@ -198,20 +198,35 @@ def main():
     del blk
     Y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     kern = cands[0]
+    fused_trial = world > 1 and args.gather == "fused" and all(k.config.epi == 1 and k.config.split_k == 1 for k in cands)
     if len(cands) > 1:
+        # Untimed selection trial.  On several GPUs the candidates are tried as the whole fused step (GEMM with
+        # the gather in its epilogue, then the barrier): the tile whose GEMM alone is fastest can lose there,
+        # because its last wave holds more of the stores that nothing is left to hide.
         trial = []
         st = torch.cuda.current_stream().cuda_stream
         for k in cands:
-            ya = torch.empty((M, plan_rows), dtype=torch.bfloat16, device=dev)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            g.dispatch(k, M, plan_rows, K, X.data_ptr(), W.data_ptr(), ya.data_ptr(), 0, st)
+            if fused_trial:
+                f = FusedNShardedGemm(k, M, N, K, rank, world)
+                run_once = lambda: f.run(X, W)
+            else:
+                ya = torch.empty((M, plan_rows), dtype=torch.bfloat16, device=dev)
+                run_once = lambda: g.dispatch(k, M, plan_rows, K, X.data_ptr(), W.data_ptr(), ya.data_ptr(), 0, st)
+            run_once()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
             e0.record()
             for _ in range(3):
-                g.dispatch(k, M, plan_rows, K, X.data_ptr(), W.data_ptr(), ya.data_ptr(), 0, st)
+                run_once()
             e1.record()
             torch.cuda.synchronize()
             trial.append(e0.elapsed_time(e1))
-            del ya
+            if fused_trial:
+                del f
+            else:
+                del ya
         t = torch.tensor(trial, device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)      # every rank must make the same choice
