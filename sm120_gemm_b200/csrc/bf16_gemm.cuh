@@ -1,17 +1,18 @@
 // Y = X * W^T for sm_100a: TMA -> 128B-swizzled shared-memory ring -> tcgen05.mma with the
 // accumulator in TMEM -> epilogue out of TMEM.  One persistent kernel template serves the
-// direct path, split-K (FP32 partials) and the dense FP8 per-tensor variant (same pipeline,
-// 1-byte elements, kind::f8f6f4).
+// direct path, split-K and stream-K (FP32 partials), the dense FP8 per-tensor variant (same
+// pipeline, 1-byte elements, kind::f8f6f4) and the block-scaled MXFP8 / MX-FP4 variants.
 //
 // Plays the role of the reference's src/bf16_gemm.cuh (kernels :259-503 and :606-828, host
 // launchers BF16GemmMMA::run :506-542 and BF16GemmMMASplitK::run :849-896), which is a
 // warpgroup mma.sync design for sm_120a.  Nothing of that structure is kept except the
 // class names of the entry points and the persistent static tile loop.
 //
-// Warp roles inside one CTA (256 threads):
+// Warp roles inside one CTA (256 threads, 384 with a second epilogue group):
 //   warp 0    TMA producer (one lane)          warp 1    tcgen05.mma issuer (one lane)
 //   warp 2    TMEM allocation / release        warp 3    idle
 //   warps 4-7 epilogue: warp w reads TMEM lanes 32*(w-4) .. +31 (one output row per thread)
+//   warps 8-11 second epilogue group, only in kernels with a single accumulator stage
 //
 // Barriers:  full[s]   TMA bytes landed           -> MMA issuer
 //            empty[s]  tcgen05.commit of stage s  -> producer
@@ -24,6 +25,11 @@
 // cta_group::2 MMA that reads both shared memories, and each CTA ends up with its 128 rows of
 // the accumulator in its own TMEM.  full[] lives in the leader and counts both CTAs' bytes;
 // empty[] / tfull[] arrivals are delivered to both CTAs by the commit.
+//
+// Two row blocks per CTA (MB = 2, 512 x 256 tiles on a pair): each CTA holds 256 rows of X per stage and
+// every K step issues two MMAs on the same B tile, one per 128-row block, into two accumulators that
+// together fill TMEM.  Shared memory then receives 96 KB of operands per 512 x 256 x 64 MACs instead of
+// 128 KB, which is what bounds the 256 x 256 tile at the power cap.
 #pragma once
 #include <cuda_bf16.h>
 
@@ -45,8 +51,9 @@ enum : int { EPI_DIRECT = 0, EPI_TMA = 1 };     // epilogue: register->global st
 
 // Where the bf16 result goes.  Normally one row-major M x N matrix.  In an N-sharded multi-GPU run
 // each rank instead stores its M x N block into columns [col_offset, col_offset + N) of the row-major
-// M x ld result on EVERY rank (plain TMA stores through NVLink peer mappings; no multicast, no loads
-// from peer memory), which fuses the all-gather of the column blocks into the epilogue.
+// M x ld result on EVERY rank, which fuses the all-gather of the column blocks into the epilogue:
+// either one TMA store per rank through NVLink peer mappings, or one multimem store per 16 bytes to the
+// NVSwitch multicast mapping of the result.  Stores only; nothing is ever loaded from peer memory.
 static constexpr int MAX_Y_PEERS = 8;
 struct YMaps {
     CUtensorMap m[MAX_Y_PEERS];
