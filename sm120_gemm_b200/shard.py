@@ -42,6 +42,18 @@ def blocked_to_row_major_index(plan_world: int, M: int, nb: int, m: int, n: int)
     return (r * M + m) * nb + j
 
 
+def destination_order(rank: int, world: int, rotate: bool = True, peers=None) -> list[int]:
+    """Ranks whose Y the peer-store epilogue writes, in store order.  Rotated: own rank first, then rank+1, ...
+    (mod world), so that ranks walking their tiles in step address different GPUs at any moment.  ``peers``
+    overrides the list (a subset is only good for timing: [rank] stores nothing remotely)."""
+    if peers is not None:
+        order = [int(r) for r in peers]
+        if not order or len(order) > 8 or any(not (0 <= r < world) for r in order) or len(set(order)) != len(order):
+            raise ValueError(f"bad destination list {order} for {world} ranks")
+        return order
+    return [(rank + i) % world if rotate else i for i in range(world)]
+
+
 class FusedNShardedGemm:
     """Per-rank GEMM whose epilogue stores its column block straight into the row-major Y of every
     rank (TMA stores over NVLink into a symmetric buffer), so the all-gather overlaps the math tile by
@@ -75,9 +87,7 @@ class FusedNShardedGemm:
         a.x_scale_f = a.w_scale_f = 1.0
         # Destination order: own buffer first, then rank+1, rank+2, ... so that at any moment the ranks
         # (which walk their tiles in step) send to eight different GPUs instead of all to the same one.
-        order = [(rank + i) % world if rotate else i for i in range(world)]
-        if peers is not None:       # subset of destinations (timing experiments: [rank] = no remote stores)
-            order = list(peers)
+        order = destination_order(rank, world, rotate, peers)
         a.y_num_peers, a.y_col_offset, a.y_ld = len(order), self.plan.row_start, N
         for i, r in enumerate(order):
             a.y_peers[i] = ptrs[r]

@@ -60,3 +60,20 @@ def test_two_rank_gather_reassembles_row_major_result(tmp_path):
     mp.spawn(_worker, args=(world, _free_port(), M, N, K, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert np.load(tmp_path / f"ok_{r}.npy")[0], f"rank {r} did not reassemble the unsharded result"
+
+
+def test_destination_order_of_the_peer_store_gather():
+    from sm120_gemm_b200.shard import destination_order
+
+    for world in (1, 2, 4, 8):
+        firsts = set()
+        for rank in range(world):
+            order = destination_order(rank, world)
+            assert order[0] == rank and sorted(order) == list(range(world))
+            firsts.add(order[1 % world])
+        assert len(firsts) == world              # at every position the ranks address different GPUs
+        assert destination_order(world - 1, world, rotate=False) == list(range(world))
+    assert destination_order(3, 8, peers=[3]) == [3]
+    for bad in ([], [9], [1, 1], list(range(9))):
+        with pytest.raises(ValueError):
+            destination_order(0, 8, peers=bad)
