@@ -113,3 +113,33 @@ def test_autotune_cache_roundtrip(tmp_path):
     d.load(str(p))
     assert d.entries == c.entries
     assert not g.AutotuneCache().load(str(tmp_path / "missing.txt"))
+
+
+def test_committed_autotune_cache_names_generated_configs():
+    """Every line of the shipped cache names a configuration the generator still produces (so the plugin
+    exists after a build) and that accepts the line's shape."""
+    from sm120_gemm_b200.gen_configs import generate_configs
+
+    names = {c.name(): c for c in generate_configs()}
+    cache = g.AutotuneCache()
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "sm120_gemm_b200", "autotune_cache.txt")
+    assert cache.load(path) and len(cache.entries) >= 10
+    for (dt, gpus, M, N, K), (cfg, ms) in cache.entries.items():
+        assert cfg.name() in names, f"{cfg.name()} is not generated any more"
+        assert names[cfg.name()].is_valid_for(M, N, K) and ms > 0
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` runs on the host cores alone and prints one JSON line with the agreed keys."""
+    import json
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "3"],
+                       capture_output=True, text=True, timeout=300, cwd=root)
+    assert r.returncode == 0, r.stderr[-500:]
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    assert d["impl"] == "reference" and d["metric"] == "gemm_tflops" and d["unit"] == "TFLOPS" and d["value"] > 0
+    assert d["higher_is_better"] is True and d["cpu_baseline"]["kind"] in ("port", "reference") and d["cpu_baseline"]["cores"] >= 1
+    assert d["e2e"]["value"] == d["value"] and d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
