@@ -38,6 +38,16 @@ int main(int argc, char **argv)
     GemmConfig sk = *GemmConfig::parse("bf16_bm128_bn128_bk64_s7_cg1_sk4_ab0_e0");
     CHECK(sk.is_valid_for(128, 4096, 14336) && !sk.is_valid_for(128, 4096, 14336 + 64) && !sk.is_valid_for(128, 128, 200));
 
+    // the shared-memory model follows the tile family: 512-row tiles hold 32 KB of X per stage (two row blocks per
+    // CTA), and with three stages four staging buffers instead of two
+    GemmConfig t4 = *GemmConfig::parse("bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1");
+    GemmConfig t3 = *GemmConfig::parse("bf16_bm512_bn256_bk64_s3_cg2_sk1_ab0_e1");
+    GemmConfig p6 = *GemmConfig::parse("bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1");
+    CHECK(t4.smem_bytes() == 4 * (32768 + 16384) + 2 * 16384 + (2 * 4 + 4) * 8 + 16 + 1024);
+    CHECK(t3.smem_bytes() == 3 * (32768 + 16384) + 4 * 16384 + (2 * 3 + 4) * 8 + 16 + 1024);
+    CHECK(p6.smem_bytes() == 6 * (16384 + 16384) + 2 * 16384 + (2 * 6 + 4) * 8 + 16 + 1024);
+    CHECK(t4.smem_bytes() <= 232448 && t4.is_valid_for(1000, 520, 1088));
+
     // cache: round trip, legacy three-field keys, malformed lines skipped, atomic replace
     const std::string path = argc > 1 ? argv[1] : "/tmp/sm100_cache_test.txt";
     {
