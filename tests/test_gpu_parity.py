@@ -17,6 +17,7 @@ from tests.gpu_util import run_bf16, to_bits, to_dev
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 BEST = "bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1"
+TALL = "bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1"      # 512 x 256 tiles: what bench.py runs on one GPU
 
 
 def dense_ok(Ybits, ref, X, W, K, min_frac=0.999):
@@ -136,13 +137,14 @@ def test_config2_decode_shapes(registry, cuda_device, shape):
     assert ran >= 8
 
 
+@pytest.mark.parametrize("name", [BEST, TALL], ids=["tile256x256", "tile512x256"])
 @pytest.mark.parametrize("size", [8192, 16384])
-def test_full_size_sampled_rows_and_properties(registry, cuda_device, size):
+def test_full_size_sampled_rows_and_properties(registry, cuda_device, size, name):
     """BASELINE config 3 (16384^3) and the 8192^3 target shape: the host oracle on 48 sampled
     rows, plus size-independent properties: exact scaling by a power of two and row-permutation
     equivariance, both bit for bit."""
     M = N = K = size
-    k = registry.find(BEST)
+    k = registry.find(name)
     gen = torch.Generator(device="cuda"); gen.manual_seed(2)
     Xd = torch.randn((M, K), device="cuda", generator=gen).to(torch.bfloat16)
     Wd = torch.randn((N, K), device="cuda", generator=gen).to(torch.bfloat16)
@@ -201,7 +203,8 @@ def test_oracle_agrees_with_reference_check_kernel(cuda_device):
     assert np.abs(got - fast).max() <= 1e-4 * max(1.0, np.abs(strict).max())
 
 
-def test_peer_destination_epilogue_single_gpu(registry, cuda_device):
+@pytest.mark.parametrize("name", [BEST, TALL], ids=["tile256x256", "tile512x256"])
+def test_peer_destination_epilogue_single_gpu(registry, cuda_device, name):
     """The fused all-gather epilogue, exercised on one GPU: two destination matrices (stand-ins for two
     ranks' Y) each receive this GEMM's block at a column offset of a wider row-major matrix; columns
     outside the block must stay untouched, also when the block's last tile is partial."""
@@ -209,7 +212,7 @@ def test_peer_destination_epilogue_single_gpu(registry, cuda_device):
 
     import sm120_gemm_b200 as g
 
-    k = registry.find(BEST)
+    k = registry.find(name)
     M, Nb, K, ld, off = 300, 328, 512, 1024, 256          # 328 = 256 + 72: partial last tile inside the destination
     X, W = o.make_inputs(M, Nb, K, seed=11)
     ref = o.gemm_bf16(X, W)
