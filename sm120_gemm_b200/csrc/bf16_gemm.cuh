@@ -142,16 +142,6 @@ struct WorkSched {
     }
 };
 
-// stream-K bookkeeping shared by the GEMM kernel and the reduce kernel
-__host__ __device__ __forceinline__ long long streamk_range_begin(long long units, int c, int num_clusters)
-{
-    return units * c / num_clusters;
-}
-__host__ __device__ __forceinline__ int streamk_owner(long long units, long long u, int num_clusters)
-{
-    return (int)(((u + 1) * num_clusters - 1) / units);   // the c with range_begin(c) <= u < range_begin(c+1)
-}
-
 // MB_ = 128-row blocks of X per CTA.  With MB_ = 2 a CTA owns 256 rows: every stage holds 32 KB of X and the
 // same B tile feeds two MMAs per K step, one per row block, each with its own accumulator.  Per flop that is a
 // quarter less operand traffic into shared memory (and out of L2) than MB_ = 1; the two 256-column accumulators
@@ -824,10 +814,7 @@ struct UmmaGemmLauncher {
         int units = sms / T::CG;
         if (units < 1) units = 1;
         if (units > total_tiles) units = total_tiles;
-        if (balance && T::SPLIT_K >= 1) {
-            const int waves = (total_tiles + units - 1) / units;
-            units = (total_tiles + waves - 1) / waves;
-        }
+        if (balance && T::SPLIT_K >= 1) units = balanced_units(total_tiles, units);
         *out = units * T::CG;
         return GEMM_OK;
     }

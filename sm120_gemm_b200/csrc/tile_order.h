@@ -24,4 +24,22 @@ TILE_HD void tile_to_mn(int tile, int num_m, int num_n, int group_n, int &mb, in
     nb = n_first + (rem - mb * width);
 }
 
+// stream-K bookkeeping shared by the GEMM kernel and the reduce kernel: `units` (tiles x k-blocks) are cut
+// into one contiguous range per CTA (pair) c, [range_begin(c), range_begin(c+1))
+TILE_HD long long streamk_range_begin(long long units, int c, int num_clusters)
+{
+    return units * c / num_clusters;
+}
+TILE_HD int streamk_owner(long long units, long long u, int num_clusters)
+{
+    return (int)(((u + 1) * num_clusters - 1) / units);   // the c with range_begin(c) <= u < range_begin(c+1)
+}
+
+// Smallest grid that walks `work` items, dealt round-robin, in as few rounds as `max_units` would.
+TILE_HD int balanced_units(int work, int max_units)
+{
+    const int waves = (work + max_units - 1) / max_units;
+    return (work + waves - 1) / waves;
+}
+
 }  // namespace sm100

@@ -93,6 +93,23 @@ int main(int argc, char **argv)
                 CHECK((int)seen.size() == num_m * num_n);
             }
 
+    // stream-K ranges tile the unit list and streamk_owner inverts streamk_range_begin
+    for (long long units : {1LL, 7LL, 148LL, 1000LL, 74LL * 256 + 5})
+        for (int nc : {1, 2, 74, 148}) {
+            CHECK(sm100::streamk_range_begin(units, 0, nc) == 0 && sm100::streamk_range_begin(units, nc, nc) == units);
+            for (long long u = 0; u < units; u += (units > 2000 ? 37 : 1)) {
+                const int c = sm100::streamk_owner(units, u, nc);
+                CHECK(c >= 0 && c < nc && sm100::streamk_range_begin(units, c, nc) <= u && u < sm100::streamk_range_begin(units, c + 1, nc));
+            }
+        }
+    // a balanced grid is never larger and needs the same number of rounds
+    for (int work : {1, 64, 74, 75, 128, 256, 512, 2048, 4097})
+        for (int mx : {1, 64, 74, 148}) {
+            const int b = sm100::balanced_units(work, mx);
+            CHECK(b >= 1 && b <= mx && b <= work && (work + b - 1) / b == (work + mx - 1) / mx);
+        }
+    CHECK(sm100::balanced_units(256, 74) == 64 && sm100::balanced_units(2048, 74) == 74 && sm100::balanced_units(128, 74) == 64);
+
     // descriptor builders: field positions
     const uint64_t d = sm100::make_smem_desc_k128(0x12400);
     CHECK((d & 0x3fff) == (0x12400 >> 4) && ((d >> 32) & 0x3fff) == 64 && ((d >> 46) & 3) == 1 && (d >> 61) == 2);
