@@ -78,7 +78,7 @@ typedef struct GemmArgs {
     void *workspace;        /* split-K partial sums; may be NULL when not needed           */
     size_t workspace_bytes;
     int32_t sm_limit;       /* 0 = all SMs; >0 = persistent grid uses at most this many    */
-    int32_t reserved;
+    int32_t reserved;       /* set to 0                                                                    */
     gemm_stream_t stream;
     /* N-sharded multi-GPU runs (TMA-store configurations only).  When y_num_peers > 0, Y is ignored and the   */
     /* M x N result is stored into columns [y_col_offset, y_col_offset + N) of the row-major M x y_ld bf16     */
@@ -94,7 +94,23 @@ typedef struct GemmArgs {
     /* store per peer, so each result byte leaves this GPU once; y_num_peers must still be > 0 and N a         */
     /* multiple of 8.  Every process bound to the multicast object must stay alive until the stores are done.  */
     void *y_multicast;
+    /* Fused output transform, honoured by the fused-epilogue plugins only (`_e2` in the name; every other plugin  */
+    /* answers GEMM_ERR_ARG when one of these is set):  D = act(alpha * (X * W^T) + beta * C + bias), written as   */
+    /* bf16, or as e4m3(D * y_scale) (saturating, round to nearest even) with max|D| folded into *amax.  No        */
+    /* counterpart in the reference, whose gemm_run has no alpha/beta/bias (src/kernel_entry.cu.in:14-16).         */
+    const void *C;          /* bf16 M x N, row pitch N, 16-byte aligned; NULL = no beta term                       */
+    const void *bias;       /* bf16, N values (one per output column), 16-byte aligned; NULL = none                */
+    float alpha;            /* e2 plugins: scales the product (set it: 0 is taken literally); others: 0 or 1       */
+    float beta;
+    int32_t activation;     /* GEMM_ACT_*                                                                          */
+    int32_t y_dtype;        /* GEMM_Y_BF16 (Y is bf16) or GEMM_Y_E4M3 (Y is M x N bytes)                           */
+    float y_scale;          /* e4m3 output: multiplies D before the conversion                                     */
+    float *amax;            /* device float, optional: atomically raised to max|D| (before y_scale); the caller    */
+                            /* zeroes it before the first launch that should count                                 */
 } GemmArgs;
+
+enum { GEMM_ACT_NONE = 0, GEMM_ACT_RELU = 1, GEMM_ACT_GELU = 2 /* erf form */, GEMM_ACT_SILU = 3 };
+enum { GEMM_Y_BF16 = 0, GEMM_Y_E4M3 = 1 };
 
 /*
  * Scale layout of the MX data types.  One ue8m0 byte scales 32 consecutive K-elements of one
@@ -107,7 +123,9 @@ typedef struct GemmArgs {
 /* Returns GEMM_OK or an error code; asynchronous on success. */
 int gemm_run_ex(const GemmArgs *args);
 
-/* The configuration name compiled into this plugin ("bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0"). */
+/* The configuration name compiled into this plugin ("bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1"):
+ * <dt>_bm<tile rows>_bn<tile columns>_bk<K per stage>_s<ring stages>_cg<CTA group>_sk<split-K, 0 = stream-K>
+ * _ab<operand swap>_e<epilogue: 0 direct stores, 1 TMA stores, 2 direct stores with the fused output transform>. */
 const char *gemm_config_name(void);
 
 /* Bytes of workspace the configuration needs for this shape (0 when it needs none).
@@ -132,8 +150,8 @@ size_t gemm_smem_bytes(void);
  * that is simply not allowed to own device memory.  Such a caller still passes X, W and Y; the
  * FP32 partial sums go into a fixed 16 MiB array compiled into the plugin
  * (GEMM_NO_ALLOC_SCRATCH_BYTES), so the shape must satisfy SPLIT_K*M*N*4 <= 16 MiB, else the
- * call fails with GEMM_ERR_WORKSPACE and launches nothing.  Plugins without split-K have no
- * scratch and answer GEMM_ERR_ARG.  The call itself performs no cudaMalloc / cudaFree.
+ * call fails with GEMM_ERR_WORKSPACE and launches nothing.  Only the bf16 split-K plugins
+ * carry the array (16 MiB per loaded plugin and GPU); every other plugin answers GEMM_ERR_ARG.  The call itself performs no cudaMalloc / cudaFree.
  *
  * The first call on each device looks up the array's device address (and does the library's
  * usual one-time kernel-attribute set-up); make that first call outside any stream capture.

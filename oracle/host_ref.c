@@ -174,6 +174,34 @@ int oracle_gemm_bf16(int M, int N, int K, const uint16_t *X, const uint16_t *W, 
     return oracle_gemm_bf16_rows(M, N, K, X, W, Y, NULL, M, strict);
 }
 
+/*
+ * Diagnostic mode: the same products (bf16 x bf16 is exact in FP32, hence in double) summed in
+ * DOUBLE, k ascending, result kept in double.  Not the reference's arithmetic (its loop adds in
+ * FP32, src/bench.cu:77-84); it exists to tell apart the two error sources when an FP32-summed
+ * reference is itself uncertain by more than the tolerance under test (K = 16384 with unit-variance
+ * inputs: the FP32 sum carries ~1e-3 of absolute noise, more than the bf16 spacing of the outputs
+ * nearest zero).  With 53 significand bits the sum of K <= 2^20 such products is exact to ~1e-13.
+ */
+void oracle_gemm_bf16_rows_f64(int N, int K, const uint16_t *X, const uint16_t *W, double *Y,
+                               const int *rows, int n_rows)
+{
+#pragma omp parallel for collapse(2) schedule(dynamic, 16)
+    for (int i = 0; i < n_rows; i++)
+        for (int c = 0; c < N; c++) {
+            const uint16_t *x = X + (size_t)(rows ? rows[i] : i) * K, *w = W + (size_t)c * K;
+            double a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+            int k = 0;
+            for (; k + 4 <= K; k += 4) {
+                a0 += (double)bf16_to_f32(x[k]) * (double)bf16_to_f32(w[k]);
+                a1 += (double)bf16_to_f32(x[k + 1]) * (double)bf16_to_f32(w[k + 1]);
+                a2 += (double)bf16_to_f32(x[k + 2]) * (double)bf16_to_f32(w[k + 2]);
+                a3 += (double)bf16_to_f32(x[k + 3]) * (double)bf16_to_f32(w[k + 3]);
+            }
+            for (; k < K; k++) a0 += (double)bf16_to_f32(x[k]) * (double)bf16_to_f32(w[k]);
+            Y[(size_t)i * N + c] = (a0 + a1) + (a2 + a3);
+        }
+}
+
 /* ------------------------------------------------------------------------------------------
  * Number formats of the quantised variants (no reference counterpart; OCP MX v1.0 and the
  * OFP8 e4m3 "fn" format: no infinities, 0x7f/0xff = NaN, max finite 448).
@@ -340,4 +368,40 @@ void oracle_int4_dequantise(const uint8_t *packed, const uint16_t *scales, int N
             dst[(size_t)n * K + k] = (float)q * bf16_to_f32(scales[(size_t)n * G + k / group]);
         }
     }
+}
+
+/*
+ * Symmetric int4 quantisation of W4A16 weights, group-wise along K: s = bf16(max|w| / 7) (1 for an
+ * all-zero group), q = clamp(rint(w / s), -8, 7), packed two per byte (low nibble = even k).
+ */
+void oracle_int4_quantise(const float *w, int N, int K, int group, uint8_t *packed, uint16_t *scales)
+{
+    int G = K / group;
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; n++) {
+        for (int g = 0; g < G; g++) {
+            const float *p = w + (size_t)n * K + (size_t)g * group;
+            float amax = 0.f;
+            for (int i = 0; i < group; i++) amax = fmaxf(amax, fabsf(p[i]));
+            uint16_t sb = f32_to_bf16(amax > 0.f ? amax / 7.0f : 1.0f);
+            scales[(size_t)n * G + g] = sb;
+            float s = bf16_to_f32(sb);
+            for (int i = 0; i < group; i += 2) {
+                float a = nearbyintf(p[i] / s), b = nearbyintf(p[i + 1] / s);
+                a = fminf(fmaxf(a, -8.f), 7.f);
+                b = fminf(fmaxf(b, -8.f), 7.f);
+                packed[((size_t)n * K + (size_t)g * group + i) / 2] = (uint8_t)(((int)a & 0xf) | (((int)b & 0xf) << 4));
+            }
+        }
+    }
+}
+
+/* number of OpenMP threads the library may use from now on (a launcher may have exported OMP_NUM_THREADS=1) */
+void oracle_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
 }

@@ -39,6 +39,7 @@ def lib() -> ctypes.CDLL:
         L.oracle_gemm_bf16_rows.argtypes = [i32, i32, i32, vp, vp, vp, vp, i32, i32]
         L.oracle_gemm_bf16_rows.restype = i32
         L.oracle_gemm_f32_rows.argtypes = [i32, i32, vp, vp, vp, vp, i32, i32]
+        L.oracle_gemm_bf16_rows_f64.argtypes = [i32, i32, vp, vp, vp, vp, i32]
         L.oracle_f32_to_bf16.argtypes = [vp, vp, sz]
         L.oracle_bf16_to_f32.argtypes = [vp, vp, sz]
         L.oracle_mx_quantise.argtypes = [vp, i32, i32, i32, vp, vp]
@@ -46,6 +47,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_e4m3_quantise.argtypes = [vp, sz, f32, vp]
         L.oracle_e4m3_dequantise.argtypes = [vp, sz, f32, vp]
         L.oracle_int4_dequantise.argtypes = [vp, vp, i32, i32, i32, vp]
+        L.oracle_int4_quantise.argtypes = [vp, i32, i32, i32, vp, vp]
+        L.oracle_set_threads.argtypes = [i32]
         for name in ("oracle_e4m3_to_f32", "oracle_e2m1_to_f32", "oracle_ue8m0_to_f32"):
             getattr(L, name).argtypes = [ctypes.c_uint8]
             getattr(L, name).restype = f32
@@ -65,6 +68,11 @@ def _p(a: np.ndarray) -> ctypes.c_void_p:
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def set_threads(n: int) -> None:
+    """OpenMP threads the oracle uses from now on (torchrun exports OMP_NUM_THREADS=1 to its workers)."""
+    lib().oracle_set_threads(int(n))
 
 
 # ----------------------------------------------------------------------------- bf16 helpers
@@ -102,6 +110,20 @@ def gemm_bf16(X: np.ndarray, W: np.ndarray, rows=None, strict: bool = False) -> 
     rc = lib().oracle_gemm_bf16_rows(M, N, K, _p(X), _p(W), _p(Y), _p(r) if r is not None else None, n, int(strict))
     if rc != 0:
         raise MemoryError("oracle scratch allocation failed")
+    return Y
+
+
+def gemm_bf16_f64(X: np.ndarray, W: np.ndarray, rows=None) -> np.ndarray:
+    """Diagnostic: ``X @ W.T`` of bf16 bit-pattern matrices with the products summed in double
+    (float64 result).  Resolves what an FP32-summed reference cannot at very large K."""
+    X = np.ascontiguousarray(X, dtype=np.uint16)
+    W = np.ascontiguousarray(W, dtype=np.uint16)
+    M, K = X.shape
+    N = W.shape[0]
+    r = None if rows is None else np.ascontiguousarray(rows, dtype=np.int32)
+    n = M if r is None else r.size
+    Y = np.empty((n, N), dtype=np.float64)
+    lib().oracle_gemm_bf16_rows_f64(N, K, _p(X), _p(W), _p(Y), _p(r) if r is not None else None, n)
     return Y
 
 
@@ -162,6 +184,17 @@ def int4_pack(q: np.ndarray) -> np.ndarray:
     return np.ascontiguousarray(u[:, 0::2] | (u[:, 1::2] << 4))
 
 
+def int4_quantise(w: np.ndarray, group: int = 128):
+    """float32 (N,K) -> (packed int4 (N,K/2), bf16 scale bits (N,K/group)): s = bf16(max|w|/7), q = clamp(rint(w/s))."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    N, K = w.shape
+    assert K % group == 0
+    packed = np.empty((N, K // 2), dtype=np.uint8)
+    scales = np.empty((N, K // group), dtype=np.uint16)
+    lib().oracle_int4_quantise(_p(w), N, K, group, _p(packed), _p(scales))
+    return packed, scales
+
+
 def int4_dequantise(packed: np.ndarray, scales_bf16: np.ndarray, group: int = 128) -> np.ndarray:
     packed = np.ascontiguousarray(packed, dtype=np.uint8)
     scales_bf16 = np.ascontiguousarray(scales_bf16, dtype=np.uint16)
@@ -183,7 +216,7 @@ def check_dense(y_bits: np.ndarray, ref: np.ndarray, K: int, max_x: float, max_w
     """The BF16 / FP8 bar: (i) max|y-ref| <= 1e-2*sqrt(K)*max|x|*max|w|;
     (ii) >= 99.9 % of outputs are one of the two bf16 neighbours of the FP32 reference."""
     y = bf16_bits_to_f32(y_bits).astype(np.float64)
-    r = ref.astype(np.float64)
+    r = ref.astype(np.float64)          # an FP32 reference, or the float64 one of gemm_bf16_f64
     err = np.abs(y - r)
     bound = 1e-2 * np.sqrt(K) * max_x * max_w
     inside = err <= bf16_ulp(ref).astype(np.float64)

@@ -19,6 +19,8 @@ from .gen_configs import DT_IDS, GemmConfig, generate_configs
 KERNEL_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "kernels")
 
 GEMM_OK = 0
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3       # GEMM_ACT_* of include/sm100_gemm.h
+Y_BF16, Y_E4M3 = 0, 1                                     # GEMM_Y_*
 ERROR_NAMES = {0: "GEMM_OK", 1: "GEMM_ERR_SHAPE", 2: "GEMM_ERR_CUDA", 3: "GEMM_ERR_DRIVER", 4: "GEMM_ERR_WORKSPACE",
                5: "GEMM_ERR_DEVICE_TIMEOUT", 6: "GEMM_ERR_ARG"}
 
@@ -48,7 +50,32 @@ class GemmArgs(ctypes.Structure):
         ("stream", ctypes.c_void_p),
         ("y_num_peers", ctypes.c_int32), ("y_col_offset", ctypes.c_int32), ("y_ld", ctypes.c_int64),
         ("y_peers", ctypes.c_void_p * 8), ("y_multicast", ctypes.c_void_p),
+        ("C", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
+        ("activation", ctypes.c_int32), ("y_dtype", ctypes.c_int32), ("y_scale", ctypes.c_float), ("amax", ctypes.c_void_p),
     ]
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        if "alpha" not in kw:
+            self.alpha = 1.0      # a plain GEMM; only the fused-epilogue plugins (e2) read it
+        if "y_scale" not in kw:
+            self.y_scale = 1.0
+
+
+class GemmWeightFileInfo(ctypes.Structure):
+    """``struct GemmWeightFileInfo`` of include/sm100_gemm_util.h (the first bytes of a weight file)."""
+
+    _fields_ = [("magic", ctypes.c_char * 8), ("version", ctypes.c_uint32), ("dtype", ctypes.c_uint32), ("layout", ctypes.c_uint32),
+                ("group", ctypes.c_uint32), ("N", ctypes.c_uint64), ("K", ctypes.c_uint64), ("elem_bytes", ctypes.c_uint64),
+                ("scale_bytes", ctypes.c_uint64), ("tensor_scale", ctypes.c_float), ("checksum", ctypes.c_uint32)]
+
+
+# every symbol include/sm100_gemm_util.h declares
+UTIL_SYMBOLS = ("gemm_interleave_blocks", "gemm_spacer", "gemm_mx_tiled_scale_bytes", "gemm_mx_scales_to_tiled",
+                "gemm_quant_e4m3_per_tensor", "gemm_quant_mx", "gemm_quant_int4_g128", "gemm_packed_weight_bytes",
+                "gemm_packed_scale_bytes", "gemm_pack_int4_host", "gemm_unpack_int4_host", "gemm_pack_fp4_host", "gemm_unpack_fp4_host",
+                "gemm_mx_scales_to_tiled_host", "gemm_mx_scales_from_tiled_host", "gemm_weight_file_write", "gemm_weight_file_info",
+                "gemm_weight_file_read")
 
 
 @dataclass
@@ -240,6 +267,19 @@ def util_lib() -> ctypes.CDLL:
         lib.gemm_mx_tiled_scale_bytes.restype = ctypes.c_size_t
         lib.gemm_mx_scales_to_tiled.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p]
         lib.gemm_mx_scales_to_tiled.restype = ctypes.c_int
+        vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+        lib.gemm_quant_e4m3_per_tensor.argtypes = [vp, vp, vp, vp, ll, vp]
+        lib.gemm_quant_mx.argtypes = [vp, vp, vp, ll, ci, ci, vp]
+        lib.gemm_quant_int4_g128.argtypes = [vp, vp, vp, ll, ci, vp]
+        for name in ("gemm_packed_weight_bytes", "gemm_packed_scale_bytes"):
+            getattr(lib, name).argtypes = [ci, ll, ci]
+            getattr(lib, name).restype = ctypes.c_size_t
+        for name in ("gemm_pack_int4_host", "gemm_unpack_int4_host", "gemm_pack_fp4_host", "gemm_unpack_fp4_host",
+                     "gemm_mx_scales_to_tiled_host", "gemm_mx_scales_from_tiled_host"):
+            getattr(lib, name).argtypes = [vp, ll, ci, vp]
+        lib.gemm_weight_file_write.argtypes = [ctypes.c_char_p, ci, ll, ci, ctypes.c_float, vp, vp]
+        lib.gemm_weight_file_info.argtypes = [ctypes.c_char_p, ctypes.POINTER(GemmWeightFileInfo)]
+        lib.gemm_weight_file_read.argtypes = [ctypes.c_char_p, vp, ctypes.c_size_t, vp, ctypes.c_size_t]
         _UTIL = lib
     return _UTIL
 

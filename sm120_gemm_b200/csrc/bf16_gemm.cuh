@@ -33,6 +33,7 @@
 #pragma once
 #include <cuda_bf16.h>
 
+#include <atomic>
 #include <cstdlib>
 
 #include "gemm_host.h"
@@ -44,10 +45,30 @@ using bf16 = __nv_bfloat16;
 
 namespace sm100 {
 
+// -DGEMM_DEBUG_BOUNDS builds check every computed TMA coordinate and every directly computed store address
+// before it is used; a violation is recorded in the device status block (code, block, offending value) and the
+// access still goes ahead only where the hardware clips it anyway (TMA boxes).  Stands in for a memory checker
+// on the ragged-shape tests; compiled out of the normal plugins.
+#ifdef GEMM_DEBUG_BOUNDS
+#define SM100_BOUNDS(cond, code, detail)                                             \
+    do {                                                                             \
+        if (!(cond) && p.status != nullptr && atomicCAS(p.status, 0u, (uint32_t)(code)) == 0u) { \
+            p.status[1] = blockIdx.x;                                                \
+            p.status[2] = (uint32_t)(detail);                                        \
+        }                                                                            \
+    } while (0)
+#else
+#define SM100_BOUNDS(cond, code, detail) do { } while (0)
+#endif
+
 // operand element kind: bf16; e4m3 with per-tensor scales; e4m3 / e2m1 with one ue8m0 scale per 32
 // K-elements of both operands (block-scaled MMA, scale factors staged in TMEM)
 enum : int { OPK_BF16 = 0, OPK_E4M3 = 1, OPK_MXFP8 = 2, OPK_MXFP4 = 3 };
-enum : int { EPI_DIRECT = 0, EPI_TMA = 1 };     // epilogue: register->global stores, or smem + TMA store
+// epilogue: register->global stores; shared memory + TMA store; register->global stores with the fused
+// output transform  D = act(alpha * acc + beta * C + bias)  and an optional e4m3 output with amax
+enum : int { EPI_DIRECT = 0, EPI_TMA = 1, EPI_FUSED = 2 };
+enum : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_SILU = 3 };   // GemmArgs.activation
+enum : int { YOUT_BF16 = 0, YOUT_E4M3 = 1 };                             // GemmArgs.y_dtype
 
 // Where the bf16 result goes.  Normally one row-major M x N matrix.  In an N-sharded multi-GPU run
 // each rank instead stores its M x N block into columns [col_offset, col_offset + N) of the row-major
@@ -71,9 +92,7 @@ struct GemmParams {
     int num_m_blocks, num_n_blocks;
     int num_k_blocks;     // per split (stream-K: per tile)
     int group_n;          // width (in N tiles) of a rasterisation band
-    int burst;            // k-blocks the producer requests together (1 .. STAGES)
     int wait_sleep_ns;    // > 0: the epilogue's wait for an accumulator and the producer's wait for a free slot back off up to this long
-    int l2_hint;          // 1: W loads evict-last, X loads evict-first (keeps a band of W panels in L2 while X streams)
     void *Y;              // bf16 output (direct epilogue)
     float *workspace;     // split-K partial sums [split][M][N]
     float alpha;          // epilogue scale (FP8 per-tensor: sx*sw)
@@ -85,6 +104,15 @@ struct GemmParams {
     // block-scaled kinds: ue8m0 scale factors in 512-byte atoms of 128 rows x 4 K-blocks,
     // atom (row/128, kblock/4) at byte ((row/128) * sf_k_atoms + kblock/4) * 512
     int sf_k_atoms;
+    // fused output transform (EPI_FUSED): D = act(alpha * acc + beta * C + bias); bf16 out, or e4m3(D * y_scale) with max|D| -> amax
+    const bf16 *C;        // M x N bf16, row pitch N; nullptr = no beta term
+    const bf16 *bias;     // N bf16 (one per output column); nullptr = none
+    float beta;
+    float y_scale;
+    float *amax;          // nullptr = not wanted
+    int act;              // ACT_*
+    int y_dtype;          // YOUT_*
+    int test_withhold_kb; // wait-expiry test build only: the producer stops before this k-block (< 0: never)
 };
 
 // One piece of work for a CTA (or CTA pair): accumulate `kb_count` k-blocks of one output tile.
@@ -201,6 +229,7 @@ struct UmmaGemmTraits {
     static_assert(CG_ == 1 || CG_ == 2, "CTA group is 1 or 2");
     static_assert(MB_ == 1 || (MB_ == 2 && SPLIT_K_ == 1 && EPI_ == EPI_TMA && !BLOCK_SCALED && ACC_STAGES == 1),
                   "two row blocks per CTA: whole-K tiles, TMA-store epilogue, dense operand kinds, one accumulator stage");
+    static_assert(EPI_ != EPI_FUSED || (SPLIT_K_ == 1 && MB_ == 1), "the fused output transform works on whole-K tiles of one row block per CTA");
     static_assert(STAGES_ >= 2, "at least two ring stages");
     static_assert(!BLOCK_SCALED || BN_ % 128 == 0, "block-scaled tiles: BN a multiple of the 128-row scale atom");
     static_assert(ACC_COLS <= 512, "TMEM has 512 columns");
@@ -296,11 +325,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             const uint32_t full_leader = (CG == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
-            const uint64_t pol_w = l2_policy_evict_last(), pol_x = l2_policy_evict_first();
             bool ok = true;
-#ifdef SM100_DEBUG_NOLOAD
-            int debug_loads = 0;
-#endif
             WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
             WorkItem w;
             while (ok && sched.next(w)) {
@@ -308,60 +333,35 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 tile_to_mn(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
                 const int row_x = mb * T::BM + (int)cta_rank * T::BM_CTA;
                 const int row_w = nb * BN + (int)cta_rank * T::BN_CTA;
-                const int kb0 = w.kb_begin;
-                const int num_kb = w.kb_count;
-                // Loads are issued in bursts of `burst` consecutive k-blocks once that many ring
-                // slots are free, so each weight row is fetched in runs of burst*128 contiguous
-                // bytes at (nearly) the same time -- kinder to DRAM pages than 128 bytes at a time.
-                for (int kb = 0; kb < num_kb && ok; kb += p.burst) {
-                    const int nb_burst = num_kb - kb < p.burst ? num_kb - kb : p.burst;
-                    int st = stage;
-                    uint32_t ph = phase;
-                    for (int d = 0; d < nb_burst; d++) {
-                        if (!mbar_wait(empty_bar(st), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, st, p.wait_sleep_ns > 128 ? 128 : p.wait_sleep_ns)) {
-                            ok = false;
-                            break;
-                        }
-                        if (++st == STAGES) { st = 0; ph ^= 1u; }
-                    }
-                    if (!ok) break;
-                    for (int d = 0; d < nb_burst; d++) {
-                        const int kx = (kb0 + kb + d) * T::BK_COORD;
-#ifdef SM100_DEBUG_NOLOAD
-                        // measurement aid (results are meaningless): after the ring's first fill no operand is
-                        // loaded any more and the stages are handed over as they are, which shows what the
-                        // MMA side sustains with no load traffic into shared memory
-                        if (debug_loads >= STAGES) {
-                            if (cta_rank == 0) mbar_arrive(full_bar(stage));
-                            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                            continue;
-                        }
-                        debug_loads++;
+                SM100_BOUNDS(row_x >= 0 && row_x < p.M + T::BM && row_w >= 0 && row_w < p.N + BN, ST_BOUNDS_LOAD_ROW, w.tile);
+                for (int kb = 0; kb < w.kb_count; kb++) {
+                    const int kx = (w.kb_begin + kb) * T::BK_COORD;
+                    // tensor-map element = bf16, or one byte for the 8- and 4-bit kinds: the box must start inside the
+                    // row (the last box may reach past its end: zero-filled) and on a 16-byte boundary
+                    SM100_BOUNDS(kx >= 0 && (long long)kx < (T::OPK == OPK_BF16 ? (long long)p.K : (long long)p.K * T::ELEM_BITS / 8) &&
+                                 (kx * (T::OPK == OPK_BF16 ? 2 : 1)) % 16 == 0, ST_BOUNDS_LOAD_K, kx);
+#ifdef SM100_TEST_WITHHOLD_STAGE
+                    // wait-expiry test build: from this k-block on nothing is requested any more, so the MMA issuer's
+                    // wait for the stage runs out (nothing is in flight then: every earlier load completes by itself)
+                    if (p.test_withhold_kb >= 0 && w.kb_begin + kb >= p.test_withhold_kb) { ok = false; break; }
 #endif
-                        if constexpr (CG == 1) {
-                            mbar_arrive_expect_tx(full_bar(stage), T::STAGE_BYTES);
-                            if (p.l2_hint) {
-                                tma_load_2d_hint(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w, pol_w);
-                                tma_load_2d_hint(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x, pol_x);
-                            } else {
-                            tma_load_2d(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w);
-                            tma_load_2d(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x);
-                            }
-                            if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, kb0 + kb + d, row_x, nb * BN, full_bar(stage));
-                        } else {
-                            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
-                            const uint32_t fb = full_leader + 8u * stage;
-                            if (p.l2_hint) {
-                                tma_load_2d_pair_hint(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w, pol_w);
-                                tma_load_2d_pair_hint(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x, pol_x);
-                            } else {
-                            tma_load_2d_pair(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w);
-                            tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x);
-                            }
-                            if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, kb0 + kb + d, row_x, nb * BN, fb);
-                        }
-                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, stage, p.wait_sleep_ns > 128 ? 128 : p.wait_sleep_ns)) {
+                        ok = false;
+                        break;
                     }
+                    if constexpr (CG == 1) {
+                        mbar_arrive_expect_tx(full_bar(stage), T::STAGE_BYTES);
+                        tma_load_2d(b_base + stage * T::B_BYTES, &tmap_w, full_bar(stage), kx, row_w);
+                        tma_load_2d(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x);
+                        if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, w.kb_begin + kb, row_x, nb * BN, full_bar(stage));
+                    } else {
+                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
+                        const uint32_t fb = full_leader + 8u * stage;
+                        tma_load_2d_pair(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w);
+                        tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x);
+                        if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, w.kb_begin + kb, row_x, nb * BN, fb);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -503,6 +503,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     tmem_ld_wait();
                     if (grow < p.M) {
                         float *dst = p.workspace + ((size_t)w.part * p.M + grow) * p.N + n0 + c0;
+                        SM100_BOUNDS(n0 + c0 >= p.N || (((size_t)w.part * p.M + grow) * p.N + n0 + c0 + 4 <= (size_t)T::SPLIT_K * p.M * p.N && w.part < T::SPLIT_K),
+                                     ST_BOUNDS_STORE, grow);
 #pragma unroll
                         for (int c = 0; c < 4; c++)
                             if (n0 + c0 + c * 4 < p.N)
@@ -557,10 +559,88 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                                 multimem_st_v4(p.y_mc + (size_t)(m0 + r) * p.y_ld + p.y_col_offset + ccol, a, b, c, d);
                         }
                     } else if (epi_tid == 0) {
+                        // stores must not start at a negative coordinate, and x must sit on a 16-byte boundary
+                        SM100_BOUNDS(m0 >= 0 && p.y_col_offset + n0 + j * 64 >= 0 && ((p.y_col_offset + n0 + j * 64) * 2) % 16 == 0, ST_BOUNDS_STORE, m0);
                         for (int t = 0; t < p.y_targets; t++) tma_store_2d(&tmap_ys.m[t], stg, p.y_col_offset + n0 + j * 64, m0);
                         tma_store_commit();
                     }
                     buf ^= 1;
+                }
+            } else if constexpr (T::EPI == EPI_FUSED) {
+                // D = act(alpha * acc + beta * C + bias) from registers; bf16 out (32 bytes per thread and step) or
+                // e4m3(D * y_scale) (16 bytes) with the running max|D| folded into *amax once per warp and tile
+                float tmax = 0.f;
+#pragma unroll 1
+                for (int c0 = eg * 16; c0 < BN; c0 += 16 * EG) {
+                    uint32_t r[16];
+                    tmem_ld_32x16(t_row + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    const int col = n0 + c0;
+                    const bool row_ok = grow < p.M;
+                    float v[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]) * p.alpha;
+                    if (p.C != nullptr && row_ok) {
+                        const bf16 *cp = p.C + (size_t)grow * p.N + col;
+#pragma unroll
+                        for (int h = 0; h < 2; h++)
+                            if (col + 8 * h < p.N) {
+                                const uint4 c4 = *reinterpret_cast<const uint4 *>(cp + 8 * h);
+                                const uint32_t cw[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                                for (int i = 0; i < 4; i++) {
+                                    v[8 * h + 2 * i] = fmaf(p.beta, __uint_as_float(cw[i] << 16), v[8 * h + 2 * i]);
+                                    v[8 * h + 2 * i + 1] = fmaf(p.beta, __uint_as_float(cw[i] & 0xffff0000u), v[8 * h + 2 * i + 1]);
+                                }
+                            }
+                    }
+                    if (p.bias != nullptr) {
+#pragma unroll
+                        for (int h = 0; h < 2; h++)
+                            if (col + 8 * h < p.N) {
+                                const uint4 b4 = __ldg(reinterpret_cast<const uint4 *>(p.bias + col + 8 * h));
+                                const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                                for (int i = 0; i < 4; i++) {
+                                    v[8 * h + 2 * i] += __uint_as_float(bw[i] << 16);
+                                    v[8 * h + 2 * i + 1] += __uint_as_float(bw[i] & 0xffff0000u);
+                                }
+                            }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        float x = v[i];
+                        if (p.act == ACT_RELU) x = fmaxf(x, 0.f);
+                        else if (p.act == ACT_GELU) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+                        else if (p.act == ACT_SILU) x = x / (1.f + __expf(-x));
+                        v[i] = x;
+                        if (row_ok && col + i < p.N) tmax = fmaxf(tmax, fabsf(x));
+                    }
+                    if (row_ok) {
+                        if (p.y_dtype == YOUT_E4M3) {
+                            uint32_t q[4];
+#pragma unroll
+                            for (int i = 0; i < 4; i++)
+                                q[i] = pack_e4m3x4(v[4 * i] * p.y_scale, v[4 * i + 1] * p.y_scale, v[4 * i + 2] * p.y_scale, v[4 * i + 3] * p.y_scale);
+                            uint8_t *dst = static_cast<uint8_t *>(p.Y) + (size_t)grow * p.N + col;
+                            if (col < p.N) *reinterpret_cast<uint2 *>(dst) = make_uint2(q[0], q[1]);
+                            if (col + 8 < p.N) *reinterpret_cast<uint2 *>(dst + 8) = make_uint2(q[2], q[3]);
+                        } else {
+                            uint32_t pk[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+                            bf16 *dst = static_cast<bf16 *>(p.Y) + (size_t)grow * p.N + col;
+                            if (col < p.N) *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            if (col + 8 < p.N) *reinterpret_cast<uint4 *>(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                        }
+                    }
+                }
+                release_acc();
+                if (p.amax != nullptr) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+                    // non-negative floats order like their bit patterns
+                    if (lane == 0 && tmax > 0.f) atomicMax(reinterpret_cast<unsigned int *>(p.amax), __float_as_uint(tmax));
                 }
             } else {
                 // bf16 straight from registers: 32 bytes per thread and step
@@ -578,6 +658,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     }
                     if (grow < p.M) {
                         bf16 *dst = static_cast<bf16 *>(p.Y) + (size_t)grow * p.N + n0 + c0;
+                        SM100_BOUNDS(n0 + c0 >= p.N || ((size_t)grow * p.N + n0 + c0 + 8 <= (size_t)p.M * p.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0),
+                                     ST_BOUNDS_STORE, grow);
                         if (n0 + c0 < p.N) *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                         if (n0 + c0 + 8 < p.N) *reinterpret_cast<uint4 *>(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                     }
@@ -705,55 +787,37 @@ inline cudaLaunchConfig_t dependent_launch_config(unsigned blocks, unsigned thre
     return cfg;
 }
 
-// L2 cache hints on the operand loads.  SM100_GEMM_L2HINT=0/1 overrides (tuning runs).
-// Back-off cap of the long waits, in ns: SM100_GEMM_WAIT_SLEEP overrides (0 = poll back to back); by
-// default 4 ns per k-block of a tile, at most 1024, so short tiles keep their latency.
+// Back-off cap of the long waits, in ns: 4 ns per k-block of a tile, at most 1024, so short tiles keep
+// their latency.
 inline int wait_sleep_ns(int num_k_blocks)
 {
-    static const int env = []() {
-        const char *e = getenv("SM100_GEMM_WAIT_SLEEP");
-        return e ? atoi(e) : -1;
-    }();
-    if (env >= 0) return env;
     const int v = num_k_blocks * 4;
     return v > 1024 ? 1024 : v;
 }
 
-inline int l2_hint_mode(int M, int N, int K)
-{
-    static const int override_h = []() {
-        const char *e = std::getenv("SM100_GEMM_L2HINT");
-        return e ? std::atoi(e) : -1;
-    }();
-    if (override_h >= 0) return override_h;
-    (void)M; (void)N; (void)K;
-    return 0;
-}
-
-// k-blocks requested together by the TMA producer.  SM100_GEMM_BURST overrides (tuning runs).
-inline int load_burst(int stages)
-{
-    static const int override_b = []() {
-        const char *e = std::getenv("SM100_GEMM_BURST");
-        return e ? std::atoi(e) : 0;
-    }();
-    int b = override_b > 0 ? override_b : 1;
-    if (b > stages) b = stages;
-    return b;
-}
-
-// Width of a rasterisation band in tiles.  SM100_GEMM_GROUP_N overrides the built-in choice
-// (read once; meant for tuning runs).
+// Width of a rasterisation band in tiles.
 inline int band_width(int bn, int mb = 1)
 {
-    static const int override_n = []() {
-        const char *e = std::getenv("SM100_GEMM_GROUP_N");
-        return e ? std::atoi(e) : 0;
-    }();
-    if (override_n > 0) return override_n;
     if (mb == 2) return 16;      // 512-row tiles: a band of 16 x 256 columns keeps a wave about square
     return bn >= 256 ? 8 : 16;
 }
+
+// Everything a launch can ask for beyond the operands; the defaults are the plain GEMM.
+struct LaunchExtras {
+    float alpha = 1.0f;                   // scales the accumulator (FP8 per-tensor: sx * sw, times the caller's alpha)
+    int sm_limit = 0;
+    const void *sf_x = nullptr, *sf_w = nullptr;   // block-scaled kinds: tiled ue8m0 scales
+    const YTarget *yt = nullptr;          // N-sharded run: store into every rank's matrix
+    // fused output transform (EPI_FUSED plugins only)
+    const void *C = nullptr;
+    const void *bias = nullptr;
+    float beta = 0.0f;
+    int act = ACT_NONE;
+    int y_dtype = YOUT_BF16;
+    float y_scale = 1.0f;
+    float *amax = nullptr;
+    int test_withhold_kb = -1;
+};
 
 template <class T>
 struct UmmaGemmLauncher {
@@ -785,12 +849,12 @@ struct UmmaGemmLauncher {
     // four rounds either way; on 64 pairs no pair idles during the fourth).
     static int grid_size(const DeviceInfo &dev, int total_tiles, int sm_limit, int *out, bool balance = false)
     {
-        static int max_clusters[MAX_DEVICES] = {0};
+        static std::atomic<int> max_clusters[MAX_DEVICES];   // 0 = not asked yet; racing first calls compute the same value
         int devid = 0;
         SM100_CUDA_TRY(cudaGetDevice(&devid));
         int sms = dev.sm_count;
         if (T::CG == 2) {
-            if (max_clusters[devid] == 0) {
+            if (max_clusters[devid].load(std::memory_order_acquire) == 0) {
                 cudaLaunchConfig_t cfg = {};
                 cfg.gridDim = dim3(dev.sm_count - dev.sm_count % 2);
                 cfg.blockDim = dim3(T::THREADS);
@@ -805,9 +869,9 @@ struct UmmaGemmLauncher {
                 int n = 0;
                 SM100_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, umma_gemm_kernel<T>, &cfg));
                 if (n <= 0) return set_error(GEMM_ERR_CUDA, "no CTA pair of this configuration fits on the device");
-                max_clusters[devid] = n;
+                max_clusters[devid].store(n, std::memory_order_release);
             }
-            sms = 2 * max_clusters[devid];
+            sms = 2 * max_clusters[devid].load(std::memory_order_acquire);
             if (sms > dev.sm_count) sms = dev.sm_count - dev.sm_count % 2;
         }
         if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
@@ -820,9 +884,12 @@ struct UmmaGemmLauncher {
     }
 
     static int run(int M, int N, int K, const void *X, const void *W, void *Y, float *workspace, size_t workspace_bytes_given,
-                   float alpha, int sm_limit, cudaStream_t stream, const void *sf_x = nullptr, const void *sf_w = nullptr,
-                   const YTarget *yt = nullptr)
+                   cudaStream_t stream, const LaunchExtras &ex = LaunchExtras())
     {
+        const float alpha = ex.alpha;
+        const int sm_limit = ex.sm_limit;
+        const void *sf_x = ex.sf_x, *sf_w = ex.sf_w;
+        const YTarget *yt = ex.yt;
         if (!can_run(M, N, K)) return set_error(GEMM_ERR_SHAPE, "shape %dx%dx%d not supported by this configuration", M, N, K);
         const bool fused_gather = yt != nullptr && yt->num_peers > 0;
         if (fused_gather) {
@@ -831,6 +898,17 @@ struct UmmaGemmLauncher {
                 return set_error(GEMM_ERR_ARG, "bad peer destination: %d peers, ld %lld, column offset %d", yt->num_peers, yt->ld, yt->col_offset);
         }
         if (!X || !W || (!Y && !fused_gather)) return set_error(GEMM_ERR_ARG, "null operand pointer");
+        const bool wants_transform = ex.C || ex.bias || ex.beta != 0.0f || ex.act != ACT_NONE || ex.y_dtype != YOUT_BF16 || ex.amax ||
+                                     (T::OPK != OPK_E4M3 && ex.alpha != 1.0f);
+        if (wants_transform && T::EPI != EPI_FUSED)
+            return set_error(GEMM_ERR_ARG, "bias / beta*C / activation / e4m3 output need a fused-epilogue configuration (e2)");
+        if (T::EPI == EPI_FUSED) {
+            if (ex.act < ACT_NONE || ex.act > ACT_SILU || (ex.y_dtype != YOUT_BF16 && ex.y_dtype != YOUT_E4M3))
+                return set_error(GEMM_ERR_ARG, "unknown activation %d or output type %d", ex.act, ex.y_dtype);
+            if (ex.beta != 0.0f && !ex.C) return set_error(GEMM_ERR_ARG, "beta != 0 needs C");
+            if (((reinterpret_cast<uintptr_t>(ex.C) | reinterpret_cast<uintptr_t>(ex.bias)) & 15u) != 0 || (reinterpret_cast<uintptr_t>(Y) & 15u) != 0)
+                return set_error(GEMM_ERR_ARG, "C, bias and Y must be 16-byte aligned");
+        }
         if (T::BLOCK_SCALED && (!sf_x || !sf_w)) return set_error(GEMM_ERR_ARG, "block-scaled configuration needs x_scale and w_scale");
         if (T::BLOCK_SCALED && ((reinterpret_cast<uintptr_t>(sf_x) | reinterpret_cast<uintptr_t>(sf_w)) & 15u))
             return set_error(GEMM_ERR_ARG, "scale arrays must be 16-byte aligned");
@@ -846,12 +924,12 @@ struct UmmaGemmLauncher {
         if (T::SMEM_ALLOC > dev->max_smem_optin)
             return set_error(GEMM_ERR_CUDA, "configuration needs %d bytes of shared memory, device allows %d", T::SMEM_ALLOC, dev->max_smem_optin);
 
-        static bool attr_set[MAX_DEVICES] = {false};
+        static std::atomic<bool> attr_set[MAX_DEVICES];   // setting the attribute twice is harmless, so a flag per device is enough
         int devid = 0;
         SM100_CUDA_TRY(cudaGetDevice(&devid));
-        if (!attr_set[devid]) {
+        if (!attr_set[devid].load(std::memory_order_acquire)) {
             SM100_CUDA_TRY(cudaFuncSetAttribute(umma_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_ALLOC));
-            attr_set[devid] = true;
+            attr_set[devid].store(true, std::memory_order_release);
         }
 
         const CUtensorMapDataType dt = (T::OPK == OPK_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
@@ -903,8 +981,6 @@ struct UmmaGemmLauncher {
         p.num_n_blocks = (N + T::BN - 1) / T::BN;
         p.num_k_blocks = ((K + T::BK - 1) / T::BK) / (T::SPLIT_K > 0 ? T::SPLIT_K : 1);
         p.group_n = band_width(T::BN, T::MB);
-        p.burst = load_burst(T::STAGES);
-        p.l2_hint = l2_hint_mode(M, N, K);
         // with a single accumulator stage the epilogue's wake-up is on the critical path of every tile
         p.wait_sleep_ns = wait_sleep_ns(T::ACC_STAGES == 1 ? (p.num_k_blocks < 16 ? p.num_k_blocks : 16) : p.num_k_blocks);
         p.Y = Y;
@@ -916,11 +992,18 @@ struct UmmaGemmLauncher {
         p.y_mc = fused_gather ? static_cast<bf16 *>(yt->multicast) : nullptr;
         p.y_ld = fused_gather ? yt->ld : 0;
         p.sf_k_atoms = (K + 127) / 128;
+        p.C = static_cast<const bf16 *>(ex.C);
+        p.bias = static_cast<const bf16 *>(ex.bias);
+        p.beta = ex.C ? ex.beta : 0.0f;
+        p.y_scale = ex.y_scale;
+        p.amax = ex.amax;
+        p.act = ex.act;
+        p.y_dtype = ex.y_dtype;
+        p.test_withhold_kb = ex.test_withhold_kb;
         const long long work = (long long)p.num_m_blocks * p.num_n_blocks * (T::SPLIT_K > 0 ? T::SPLIT_K : p.num_k_blocks);
         int grid = 0;
         // compute-bound shapes only: a memory-bound one (M <= 128 rows) wants every SM's loads in flight
-        static const bool balance_on = []() { const char *e = std::getenv("SM100_GEMM_BALANCE"); return !e || std::atoi(e) != 0; }();
-        rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &grid, balance_on && M >= 512);
+        rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &grid, M >= 512);
         if (rc != GEMM_OK) return rc;
         if (T::SPLIT_K == 0 && grid > STREAMK_MAX_CTAS) grid = STREAMK_MAX_CTAS - STREAMK_MAX_CTAS % T::CG;
 
@@ -960,28 +1043,42 @@ struct UmmaGemmLauncher {
 
 }  // namespace sm100
 
-// The reference's two entry-point class templates (src/bf16_gemm.cuh:193 and :549), kept by
-// name with a static run() of the same argument order; the template parameters are the
-// sm_100 configuration space (tile rows are 128 x CTA_GROUP, BK is fixed by the 128-byte
-// swizzle span).  run() returns a GEMM_* status instead of exiting or throwing.
+// The reference's two entry-point class templates (src/bf16_gemm.cuh:193 and :549), kept by name with a
+// static run() of the same argument order; every bf16 plugin reaches its kernel through one of them (as the
+// reference's entry template does, src/kernel_entry.cu.in:20-26).  The template parameters are the sm_100
+// configuration space: tile rows BM = 128 x CTA_GROUP x (row blocks per CTA), BK fixed by the 128-byte swizzle
+// span.  run() returns a GEMM_* status instead of exiting or throwing; run_ex() is run() with the arguments
+// the reference does not have (SM limit, peer destinations, output transform).
 template <int BM, int BN, int BK, int NUM_STAGES, int CTA_GROUP = 1, int EPI = sm100::EPI_TMA>
 struct BF16GemmMMA {
-    using Traits = sm100::UmmaGemmTraits<sm100::OPK_BF16, BN, NUM_STAGES, CTA_GROUP, 1, EPI>;
-    static_assert(BM == Traits::BM && BK == Traits::BK, "BM must be 128*CTA_GROUP and BK 64 for bf16");
-    static int run(int M, int N, int K, const bf16 *X, const bf16 *W, bf16 *Y, cudaStream_t stream, int sm_limit = 0)
+    static constexpr int MB = BM / (128 * CTA_GROUP);
+    using Traits = sm100::UmmaGemmTraits<sm100::OPK_BF16, BN, NUM_STAGES, CTA_GROUP, 1, EPI, MB>;
+    using Launcher = sm100::UmmaGemmLauncher<Traits>;
+    static_assert(BM == Traits::BM && BK == Traits::BK, "BM must be 128*CTA_GROUP*(1|2) and BK 64 for bf16");
+    static int run(int M, int N, int K, const bf16 *X, const bf16 *W, bf16 *Y, cudaStream_t stream)
     {
-        return sm100::UmmaGemmLauncher<Traits>::run(M, N, K, X, W, Y, nullptr, 0, 1.0f, sm_limit, stream);
+        return Launcher::run(M, N, K, X, W, Y, nullptr, 0, stream);
+    }
+    static int run_ex(int M, int N, int K, const bf16 *X, const bf16 *W, void *Y, cudaStream_t stream, const sm100::LaunchExtras &ex)
+    {
+        return Launcher::run(M, N, K, X, W, Y, nullptr, 0, stream, ex);
     }
 };
 
+// SPLIT_K > 1: equal K slices, FP32 partials in `workspace`, reduce kernel; SPLIT_K == 0: stream-K.
 template <int BM, int BN, int BK, int NUM_STAGES, int CTA_GROUP, int SPLIT_K>
 struct BF16GemmMMASplitK {
     using Traits = sm100::UmmaGemmTraits<sm100::OPK_BF16, BN, NUM_STAGES, CTA_GROUP, SPLIT_K, sm100::EPI_DIRECT>;
+    using Launcher = sm100::UmmaGemmLauncher<Traits>;
     static_assert(BM == Traits::BM && BK == Traits::BK, "BM must be 128*CTA_GROUP and BK 64 for bf16");
     // workspace: >= SPLIT_K*M*N floats, caller-owned, need not be zeroed (as src/bf16_gemm.cuh:601)
-    static int run(int M, int N, int K, const bf16 *X, const bf16 *W, bf16 *Y, float *workspace, cudaStream_t stream,
-                   size_t workspace_bytes = 0, int sm_limit = 0)
+    static int run(int M, int N, int K, const bf16 *X, const bf16 *W, bf16 *Y, float *workspace, cudaStream_t stream)
     {
-        return sm100::UmmaGemmLauncher<Traits>::run(M, N, K, X, W, Y, workspace, workspace_bytes, 1.0f, sm_limit, stream);
+        return Launcher::run(M, N, K, X, W, Y, workspace, 0, stream);
+    }
+    static int run_ex(int M, int N, int K, const bf16 *X, const bf16 *W, void *Y, float *workspace, size_t workspace_bytes,
+                      cudaStream_t stream, const sm100::LaunchExtras &ex)
+    {
+        return Launcher::run(M, N, K, X, W, Y, workspace, workspace_bytes, stream, ex);
     }
 };

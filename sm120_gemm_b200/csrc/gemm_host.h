@@ -10,6 +10,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -60,7 +61,7 @@ inline void clear_error()
 
 // ---------------------------------------------------------------------------------- device
 struct DeviceInfo {
-    bool ready = false;
+    std::atomic<bool> ready{false};   // set (release) after every other field; readers load it (acquire) first
     int sm_count = 0;
     int max_smem_optin = 0;
     int cc_major = 0;
@@ -80,9 +81,9 @@ inline int device_info(DeviceInfo **out)
     SM100_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MAX_DEVICES) return set_error(GEMM_ERR_ARG, "device ordinal %d out of range", dev);
     DeviceInfo &d = infos[dev];
-    if (!d.ready) {
+    if (!d.ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(mu);
-        if (!d.ready) {
+        if (!d.ready.load(std::memory_order_relaxed)) {
             SM100_CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
             SM100_CUDA_TRY(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
             SM100_CUDA_TRY(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
@@ -92,7 +93,7 @@ inline int device_info(DeviceInfo **out)
             SM100_CUDA_TRY(cudaGetSymbolAddress(&p, g_status_block));
             SM100_CUDA_TRY(cudaMemset(p, 0, sizeof(uint32_t) * 4));
             d.status = static_cast<uint32_t *>(p);
-            d.ready = true;
+            d.ready.store(true, std::memory_order_release);
         }
     }
     *out = &d;

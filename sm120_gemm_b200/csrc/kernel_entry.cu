@@ -4,7 +4,7 @@
 // Same role as the reference's src/kernel_entry.cu.in:5-27 (a CMake-configured template with
 // eight @VAR@ constants and one exported gemm_run); here the build passes
 //   -DGEMM_DT=<0..4> -DGEMM_BN=<64|128|192|256> -DGEMM_STAGES=<n> -DGEMM_CG=<1|2>
-//   -DGEMM_SK=<split-K> -DGEMM_AB=<0|1 operand swap> -DGEMM_EPI=<0|1> -DGEMM_MB=<1|2 row blocks per CTA>
+//   -DGEMM_SK=<split-K> -DGEMM_AB=<0|1 operand swap> -DGEMM_EPI=<0|1|2> -DGEMM_MB=<1|2 row blocks per CTA>
 #include "bf16_gemm.cuh"
 #include "w4a16_gemm.cuh"
 
@@ -32,9 +32,20 @@ constexpr int BM = 128 * CG * MB;
 static_assert(AB == 1 && SK == 0 && CG == 1 && EPI == 0, "W4A16 plugins are <dt>_bm128_bn<MPAD>_bk64_s<S>_cg1_sk0_ab1_e0");
 using Traits = sm100::W4A16Traits<BN, STAGES>;
 using Launcher = sm100::W4A16Launcher<Traits>;
+#elif GEMM_DT == 0
+// BF16: through the reference's two entry-point classes, chosen at compile time exactly as its entry template
+// does (src/kernel_entry.cu.in:20-26): no split -> BF16GemmMMA, split-K (or stream-K) -> BF16GemmMMASplitK
+static_assert(AB == 0, "operand swap is not part of this kernel");
+#if GEMM_SK == 1
+using Entry = BF16GemmMMA<BM, BN, 64, STAGES, CG, EPI>;
+#else
+using Entry = BF16GemmMMASplitK<BM, BN, 64, STAGES, CG, SK>;
+#endif
+using Traits = Entry::Traits;
+using Launcher = Entry::Launcher;
 #else
 static_assert(AB == 0, "operand swap is not part of this kernel");
-constexpr int OPK = DT == GEMM_DT_BF16 ? sm100::OPK_BF16 : DT == GEMM_DT_FP8 ? sm100::OPK_E4M3 : DT == GEMM_DT_MXFP8 ? sm100::OPK_MXFP8 : sm100::OPK_MXFP4;
+constexpr int OPK = DT == GEMM_DT_FP8 ? sm100::OPK_E4M3 : DT == GEMM_DT_MXFP8 ? sm100::OPK_MXFP8 : sm100::OPK_MXFP4;
 using Traits = sm100::UmmaGemmTraits<OPK, BN, STAGES, CG, SK, EPI, MB>;
 using Launcher = sm100::UmmaGemmLauncher<Traits>;
 #endif
@@ -46,8 +57,10 @@ const char *const kConfigName = GEMM_STR(GEMM_NAME);
 // Scratch for gemm_run_no_alloc: lives in the plugin's own device image, so using it needs no
 // allocation call at all.  16 MiB = room for SPLIT_K*M*N <= 4 Mi FP32 partial sums (for example
 // 128 x 4096 outputs split 8 ways).  Every GPU that loads this plugin holds the array until the
-// process exits.  Only split-K configurations have scratch to place here.
-#if GEMM_SK > 1
+// process exits.  Only the bf16 split-K configurations have the array (gemm_run_no_alloc takes bf16
+// operands; compiled into the others it would be 16 MiB per loaded plugin and GPU that nothing can use).
+#define GEMM_HAS_STATIC_SCRATCH (GEMM_SK > 1 && GEMM_DT == 0)
+#if GEMM_HAS_STATIC_SCRATCH
 constexpr size_t kStaticScratchBytes = GEMM_NO_ALLOC_SCRATCH_BYTES;
 static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
 #else
@@ -61,12 +74,19 @@ extern "C" {
 void gemm_run(int M, int N, int K, const void *X, const void *W, void *Y, float *workspace, gemm_stream_t stream)
 {
     sm100::clear_error();
-    if (DT != GEMM_DT_BF16) {
-        sm100::set_error(GEMM_ERR_ARG, "gemm_run takes bf16 operands; %s needs gemm_run_ex", kConfigName);
-        return;
-    }
-#if GEMM_DT != 3
-    Launcher::run(M, N, K, X, W, Y, workspace, 0, 1.0f, 0, stream);
+#if GEMM_DT == 0
+    auto *x = static_cast<const bf16 *>(X);
+    auto *w = static_cast<const bf16 *>(W);
+    auto *y = static_cast<bf16 *>(Y);
+#if GEMM_SK == 1
+    (void)workspace;
+    Entry::run(M, N, K, x, w, y, stream);
+#else
+    Entry::run(M, N, K, x, w, y, workspace, stream);
+#endif
+#else
+    (void)M; (void)N; (void)K; (void)X; (void)W; (void)Y; (void)workspace; (void)stream;
+    sm100::set_error(GEMM_ERR_ARG, "gemm_run takes bf16 operands; %s needs gemm_run_ex", kConfigName);
 #endif
 }
 
@@ -77,18 +97,46 @@ int gemm_run_ex(const GemmArgs *a)
     if ((int)a->dtype != DT) return sm100::set_error(GEMM_ERR_ARG, "dtype %u does not match plugin %s", a->dtype, kConfigName);
 #if GEMM_DT == 3
     if (a->y_num_peers > 0) return sm100::set_error(GEMM_ERR_ARG, "peer destinations are not supported by %s", kConfigName);
+    if (a->C || a->bias || a->amax || a->activation || a->y_dtype) return sm100::set_error(GEMM_ERR_ARG, "%s has no fused output transform", kConfigName);
     return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, a->w_scale, a->group_size, static_cast<float *>(a->workspace), a->workspace_bytes,
                          a->sm_limit, a->stream);
 #else
-    const float alpha = (DT == GEMM_DT_FP8) ? a->x_scale_f * a->w_scale_f : 1.0f;
     sm100::YTarget yt;
     yt.peers = a->y_peers;
     yt.num_peers = a->y_num_peers;
     yt.multicast = a->y_multicast;
     yt.ld = a->y_ld;
     yt.col_offset = a->y_col_offset;
-    return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, static_cast<float *>(a->workspace), a->workspace_bytes, alpha,
-                         a->sm_limit, a->stream, a->x_scale, a->w_scale, a->y_num_peers > 0 ? &yt : nullptr);
+    sm100::LaunchExtras ex;
+    // alpha is an argument of the fused-epilogue plugins (e2) only; the others compute the plain product
+    const float user_alpha = (EPI == sm100::EPI_FUSED) ? a->alpha : 1.0f;
+    if (EPI != sm100::EPI_FUSED && a->alpha != 0.0f && a->alpha != 1.0f)
+        return sm100::set_error(GEMM_ERR_ARG, "alpha = %g needs a fused-epilogue configuration (e2); %s computes X*W^T as is", a->alpha, kConfigName);
+    ex.alpha = (DT == GEMM_DT_FP8 ? a->x_scale_f * a->w_scale_f : 1.0f) * user_alpha;
+    ex.sm_limit = a->sm_limit;
+    ex.sf_x = a->x_scale;
+    ex.sf_w = a->w_scale;
+    ex.yt = a->y_num_peers > 0 ? &yt : nullptr;
+    ex.C = a->C;
+    ex.bias = a->bias;
+    ex.beta = a->beta;
+    ex.act = a->activation;
+    ex.y_dtype = a->y_dtype;
+    ex.y_scale = a->y_scale;
+    ex.amax = a->amax;
+#ifdef SM100_TEST_WITHHOLD_STAGE
+    ex.test_withhold_kb = a->reserved - 1;      // wait-expiry test build: reserved = first withheld k-block + 1 (0 = none)
+#endif
+#if GEMM_DT == 0
+#if GEMM_SK == 1
+    return Entry::run_ex(a->M, a->N, a->K, static_cast<const bf16 *>(a->X), static_cast<const bf16 *>(a->W), a->Y, a->stream, ex);
+#else
+    return Entry::run_ex(a->M, a->N, a->K, static_cast<const bf16 *>(a->X), static_cast<const bf16 *>(a->W), a->Y,
+                         static_cast<float *>(a->workspace), a->workspace_bytes, a->stream, ex);
+#endif
+#else
+    return Launcher::run(a->M, a->N, a->K, a->X, a->W, a->Y, static_cast<float *>(a->workspace), a->workspace_bytes, a->stream, ex);
+#endif
 #endif
 }
 
@@ -102,7 +150,7 @@ const char *gemm_last_error_message(void) { return sm100::error_state().msg; }
 int gemm_run_no_alloc(int M, int N, int K, const void *X, const void *W, void *Y, gemm_stream_t stream)
 {
     sm100::clear_error();
-#if GEMM_SK > 1
+#if GEMM_HAS_STATIC_SCRATCH
     if (DT != GEMM_DT_BF16) return sm100::set_error(GEMM_ERR_ARG, "gemm_run_no_alloc takes bf16 operands; %s does not", kConfigName);
     if (!Launcher::can_run(M, N, K)) return sm100::set_error(GEMM_ERR_SHAPE, "shape %dx%dx%d not supported by %s", M, N, K, kConfigName);
     const size_t need = Launcher::workspace_bytes(M, N, K);
@@ -130,7 +178,7 @@ int gemm_run_no_alloc(int M, int N, int K, const void *X, const void *W, void *Y
     }
     // every partial sum the reduce kernel reads is written by this call's GEMM kernel first, so
     // nothing in the array has to start at zero and the previous call's contents do not matter
-    return Launcher::run(M, N, K, X, W, Y, scratch, kStaticScratchBytes, 1.0f, 0, stream);
+    return Launcher::run(M, N, K, X, W, Y, scratch, kStaticScratchBytes, stream);
 #else
     (void)M; (void)N; (void)K; (void)X; (void)W; (void)Y; (void)stream;
     return sm100::set_error(GEMM_ERR_ARG, "gemm_run_no_alloc: %s has no built-in scratch array; call gemm_run", kConfigName);

@@ -18,7 +18,10 @@ namespace sm100 {
 // 1.0-1.97 GHz the part runs at (the longest legitimate wait is one output tile's main loop,
 // well under 10 ms even for K = 64k).  The SM's own cycle counter is used because it is cheap
 // to read; %globaltimer is not.
-static constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;
+#ifndef SM100_WAIT_LIMIT_CYCLES
+#define SM100_WAIT_LIMIT_CYCLES 3000000000ll
+#endif
+static constexpr long long WAIT_LIMIT_CYCLES = SM100_WAIT_LIMIT_CYCLES;   // the wait-expiry test plugin is built with a short limit
 
 // Codes written to the device status word by a wait that gave up.
 enum : uint32_t {
@@ -28,6 +31,10 @@ enum : uint32_t {
     ST_TIMEOUT_MMA_ACC = 3,    // MMA issuer waiting for a drained accumulator
     ST_TIMEOUT_EPILOGUE = 4,   // epilogue waiting for a finished accumulator
     ST_TIMEOUT_DEQUANT = 5,    // dequantiser warps (W4A16)
+    // -DGEMM_DEBUG_BOUNDS builds only: a computed coordinate or address failed its check
+    ST_BOUNDS_LOAD_ROW = 16,   // TMA load: row coordinate outside the matrix (+ one tile of slack)
+    ST_BOUNDS_LOAD_K = 17,     // TMA load: K coordinate outside the row or off a 16-byte boundary
+    ST_BOUNDS_STORE = 18,      // store: address outside the destination or misaligned
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -124,11 +131,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-#ifdef SM100_SPIN_TEST_WAIT
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(done)
@@ -189,36 +192,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
-        : "memory");
-}
-
-// L2 eviction-priority policies for loads that carry a cache hint
-__device__ __forceinline__ uint64_t l2_policy_evict_last()
-{
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first()
-{
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-
-// tile loads with an L2 cache hint (one CTA / CTA pair)
-__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, uint64_t policy)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy)
-        : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst, const CUtensorMap *map, uint32_t cluster_bar, int x, int y, uint64_t policy)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
-        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y), "l"(policy)
         : "memory");
 }
 
@@ -463,6 +436,15 @@ __device__ __forceinline__ void multimem_st_v4(void *mc_addr, uint32_t a, uint32
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// four floats -> four e4m3 bytes (round to nearest even, saturating to +-448), a in the lowest byte
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d)
+{
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)

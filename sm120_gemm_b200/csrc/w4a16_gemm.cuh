@@ -357,12 +357,12 @@ struct W4A16Launcher {
         DeviceInfo *dev = nullptr;
         int rc = device_info(&dev);
         if (rc != GEMM_OK) return rc;
-        static bool attr_set[MAX_DEVICES] = {false};
+        static std::atomic<bool> attr_set[MAX_DEVICES];
         int devid = 0;
         SM100_CUDA_TRY(cudaGetDevice(&devid));
-        if (!attr_set[devid]) {
+        if (!attr_set[devid].load(std::memory_order_acquire)) {
             SM100_CUDA_TRY(cudaFuncSetAttribute(w4a16_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_ALLOC));
-            attr_set[devid] = true;
+            attr_set[devid].store(true, std::memory_order_release);
         }
         CUtensorMap tx, tw;
         rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, X, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, T::MPAD, CU_TENSOR_MAP_SWIZZLE_128B);

@@ -15,7 +15,8 @@ shared-memory cap for the mma.sync kernel), re-derived for the tcgen05 design:
   sk       split-K factor (FP32 partials + reduce kernel); 0 = stream-K: the tiles x k-blocks work is
            cut into one equal contiguous range per CTA, partial tiles are summed by a fix-up kernel
   ab       operand swap for small M (W rows on the 128 accumulator lanes)
-  e        epilogue: 0 = registers -> global, 1 = swizzled shared memory -> TMA store
+  e        epilogue: 0 = registers -> global, 1 = swizzled shared memory -> TMA store,
+           2 = registers -> global with the fused output transform act(alpha*acc + beta*C + bias), bf16 or e4m3 out
 
 Name:  <dt>_bm<bm>_bn<bn>_bk<bk>_s<s>_cg<cg>_sk<sk>_ab<ab>_e<e>
 
@@ -166,6 +167,9 @@ def generate_configs(max_smem: int = MAX_SMEM, dts=("bf16", "fp8", "mxfp8", "w4a
             c = GemmConfig(dt, 512, 256, bk, s, 2, 1, 0, 1)
             if c.smem_bytes() <= max_smem:
                 out.append(c)
+        # fused output transform (bias, alpha/beta, activation, e4m3 output with amax): one small and one large tile
+        for cg, bn in ((1, 128), (2, 256)):
+            out.append(GemmConfig(dt, 128 * cg, bn, bk, min(max_stages(dt, bn, cg, 1, 2, max_smem), 8), cg, 1, 0, 2))
         # split-K: for shapes with too few output tiles to fill 148 SMs (decode, M <= 128)
         for cg, bn in ((1, 64), (1, 128), (1, 256), (2, 128), (2, 256)):
             for sk in (2, 4, 7, 8, 16):
@@ -186,8 +190,22 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--max-smem-kb", type=int, default=MAX_SMEM // 1024)
     ap.add_argument("--dt", default="bf16,fp8,mxfp8,w4a4,w4a16")
+    ap.add_argument("--output", default=None,
+                    help="write a CMake fragment  set(GEMM_CONFIGS \"name|DT|BN|STAGES|CG|SK|AB|EPI|MB;...\")  instead of printing names "
+                         "(the reference's generator does the same for its CMakeLists.txt, scripts/gen_configs.py:52-75)")
     args = ap.parse_args()
-    for c in generate_configs(args.max_smem_kb * 1024, tuple(args.dt.split(","))):
+    configs = generate_configs(args.max_smem_kb * 1024, tuple(args.dt.split(",")))
+    if args.output:
+        import os
+
+        os.makedirs(os.path.dirname(os.path.abspath(args.output)), exist_ok=True)
+        items = [f"{c.name()}|{DT_IDS[c.dt]}|{c.bn}|{c.num_stages}|{c.cg}|{c.split_k}|{c.swap_ab}|{c.epi}|{c.mb}" for c in configs]
+        with open(args.output, "w") as f:
+            f.write("# generated by gen_configs.py -- one entry per kernel plugin\n")
+            f.write('set(GEMM_CONFIGS "' + ";".join(items) + '")\n')
+        print(f"wrote {len(items)} configurations to {args.output}")
+        return
+    for c in configs:
         print(c.name())
 
 

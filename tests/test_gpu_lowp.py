@@ -123,6 +123,49 @@ def test_mxfp8(registry, cuda_device, shape):
     assert ran >= 5
 
 
+def test_mxfp8_8192_sampled_rows(registry, cuda_device):
+    """BASELINE config 4(b) at full size: MXFP8 8192^3 with real quantised data (block magnitudes spread over
+    2^-3..2^3 so a misplaced scale cannot hide), 40 sampled rows against the host oracle, dense bar.
+    Runs the one-CTA and the CTA-pair tile."""
+    M = N = K = 8192
+    qx, sx, qw, sw = mx_case(M, N, K, 8, seed=3)
+    rows = np.unique(np.concatenate([[0, 127, 128, 255, 256, M - 1], np.random.default_rng(1).integers(0, M, 34)]))
+    dx, dw = o.mx_dequantise(qx[rows], sx[rows], 8), o.mx_dequantise(qw, sw, 8)
+    ref = o.gemm_f32(dx, dw)
+    Xd, Wd, SXd, SWd = torch.from_numpy(qx).cuda(), torch.from_numpy(qw).cuda(), to_tiled_dev(sx, K), to_tiled_dev(sw, K)
+    sel = torch.from_numpy(rows).cuda()
+    ran = 0
+    for k in registry.kernels:
+        if k.config.dt != "mxfp8" or k.config.split_k != 1 or k.config.epi != 1:
+            continue
+        Y = run_ex(k, M, N, K, Xd, Wd, x_scale=SXd, w_scale=SWd)
+        r = o.check_dense(to_bits(Y[sel]), ref, K, float(np.abs(dx).max()), float(np.abs(dw).max()))
+        assert r["max_abs_err"] <= r["bound"] and r["frac_within_bf16_rounding"] >= 0.999, (k.config.name(), r)
+        ran += 1
+    assert ran >= 2
+
+
+@pytest.mark.parametrize("M", [1, 16, 128])
+def test_w4a4_config5_shapes(registry, cuda_device, M):
+    """BASELINE config 5(b) at its stated shape: M in {1, 16, 128}, N = 28672, K = 8192, MX-FP4 on both
+    operands, full host oracle (dequantise, FP32 GEMM), every w4a4 plugin that takes the shape."""
+    N, K = 28672, 8192
+    qx, sx, qw, sw = mx_case(M, N, K, 4, seed=4)
+    dx, dw = o.mx_dequantise(qx, sx, 4), o.mx_dequantise(qw, sw, 4)
+    ref = o.gemm_f32(dx, dw)
+    Xd, Wd, SXd, SWd = torch.from_numpy(qx).cuda(), torch.from_numpy(qw).cuda(), to_tiled_dev(sx, K), to_tiled_dev(sw, K)
+    ran = 0
+    for k in registry.kernels:
+        if k.config.dt != "w4a4" or not k.can_run(M, N, K):
+            continue
+        Y = to_bits(run_ex(k, M, N, K, Xd, Wd, x_scale=SXd, w_scale=SWd))
+        assert not np.isnan(o.bf16_bits_to_f32(Y)).any(), k.config.name()
+        r = o.check_quantised(Y, ref)
+        assert r["ok"], (k.config.name(), M, r)
+        ran += 1
+    assert ran >= 5
+
+
 @pytest.mark.parametrize("shape", [(128, 128, 256), (128, 256, 512), (16, 512, 1024), (1, 256, 2048), (100, 136, 512), (512, 1024, 2048)])
 def test_w4a4_mxfp4(registry, cuda_device, shape):
     """BASELINE config 5(b): e2m1 elements (two per byte), ue8m0 scale per 32 K-elements."""
