@@ -26,7 +26,10 @@ sys.path.insert(0, ROOT)
 
 M = N = K = 16384
 WORKLOAD = "bf16 gemm Y=X*W^T M=N=K=16384, X,W~N(0,1) seed 2, fp32 accumulate, bf16 out (BASELINE config 3)"
-DEFAULT_KERNELS = ["bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1", "bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1"]
+# the second tile family always joins the untimed selection trial: on several GPUs the tile whose GEMM alone is
+# fastest can lose once the gather rides in its epilogue
+ALTERNATE_FAMILY = ["bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1", "bf16_bm256_bn256_bk64_s6_cg2_sk1_ab0_e1"]
+CHECK_ROWS = 32
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel at this workload,
 # from the ncu capture summarised under profiles/ (None until captured)
 NCU_TRAFFIC_BYTES = {   # profiles/kernel_families_limited_metrics.md, 16384^3 rows
@@ -76,12 +79,30 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
 
 
+def host_threads() -> int:
+    """Host hardware threads this process may use."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def load_oracle(threads: int):
+    """The CPU oracle with an explicit OpenMP thread count: a launcher (torch.distributed.run) exports
+    OMP_NUM_THREADS=1 to its workers, which would otherwise make the host arm a single-core run."""
+    os.environ["OMP_NUM_THREADS"] = str(threads)
+    from oracle import oracle as o
+
+    o.set_threads(threads)
+    return o
+
+
 def cpu_baseline(seconds_target: float = 12.0):
     """Times the CPU oracle (restatement of the reference's FP32 loop, src/bench.cu:77-84) on a
     row slab of the same 16384^3 workload, all host threads."""
     import numpy as np
 
-    from oracle import oracle as o
+    o = load_oracle(host_threads())
 
     rng = np.random.default_rng(2)
     W = o.f32_to_bf16_bits(rng.standard_normal((N, K), dtype=np.float32))
@@ -104,8 +125,7 @@ def run_reference_arm(args):
         return
     import numpy as np
 
-    from oracle import oracle as o
-
+    o = load_oracle(host_threads())
     base, W = cpu_baseline(4.0)
     rng = np.random.default_rng(2)
     rows = 256
@@ -127,14 +147,65 @@ def run_reference_arm(args):
     }))
 
 
+def make_inputs(torch, dev, rank, world):
+    """X (full) and this rank's rows of W, N(0,1) bf16 from fixed seeds: every rank draws the same two streams
+    and keeps its own weight rows, so W never crosses GPUs.  `w_rows(r0, r1)` redraws any rows of the full W
+    (for the result check)."""
+    plan_rows = N // world
+    gen = torch.Generator(device=dev); gen.manual_seed(2)
+    X = torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16)
+    chunk = 2048
+
+    def w_blocks():
+        g2 = torch.Generator(device=dev); g2.manual_seed(1002)
+        for r0 in range(0, N, chunk):
+            yield r0, torch.randn((chunk, K), device=dev, generator=g2).to(torch.bfloat16)
+
+    W = torch.empty((plan_rows, K), dtype=torch.bfloat16, device=dev)
+    for r0, blk in w_blocks():
+        lo, hi = max(r0, rank * plan_rows), min(r0 + chunk, (rank + 1) * plan_rows)
+        if lo < hi:
+            W[lo - rank * plan_rows:hi - rank * plan_rows] = blk[lo - r0:hi - r0]
+    return X, W, w_blocks
+
+
+def check_result(torch, dist, Y, X, w_blocks, rank, world):
+    """Outside the timed region: CHECK_ROWS sampled rows of this rank's full Y (its own and every other rank's
+    column blocks) against the CPU oracle's FP32 rows, under the dense tolerance.  The verdict is all-reduced so
+    every rank stops together.  (The oracle is used as the checker only; nothing timed touches it.)"""
+    import numpy as np
+
+    o = load_oracle(max(1, host_threads() // world))
+    rows = np.unique(np.concatenate([[0, M - 1], np.random.default_rng(100 + rank).integers(0, M, CHECK_ROWS - 2)]))
+    sel = torch.from_numpy(rows).to(Y.device)
+    Xs = X[sel].view(torch.int16).cpu().numpy().view(np.uint16)
+    Wh = np.empty((N, K), dtype=np.uint16)
+    for r0, blk in w_blocks():
+        Wh[r0:r0 + blk.shape[0]] = blk.view(torch.int16).cpu().numpy().view(np.uint16)
+    ref = o.gemm_bf16(Xs, Wh)
+    yb = Y[sel].view(torch.int16).cpu().numpy().view(np.uint16)
+    r = o.check_dense(yb, ref, K, float(np.abs(o.bf16_bits_to_f32(Xs)).max()), float(np.abs(o.bf16_bits_to_f32(Wh)).max()))
+    # bar (ii) at K = 16384 with unit-variance inputs sits at 99.89 % for any FP32-accumulating tensor-core GEMM
+    # (cuBLAS included; tests/test_gpu_parity.py measures both against a double-precision sum), so the gate here is 99.8 %
+    ok = bool(not np.isnan(o.bf16_bits_to_f32(yb)).any() and r["max_abs_err"] <= r["bound"] and r["frac_within_bf16_rounding"] >= 0.998)
+    frac = r["frac_within_bf16_rounding"]
+    if world > 1:
+        t = torch.tensor([1.0 if ok else 0.0, frac], device=Y.device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok, frac = bool(t[0].item() > 0.5), float(t[1].item())
+    return {"rows": int(rows.size) * world, "columns": N, "frac_within_bf16_rounding": frac, "max_abs_err": r["max_abs_err"], "bound": r["bound"],
+            "against": "CPU oracle (FP32 loop of the reference's check kernel), every rank, before the timed region", "ok": ok}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--kernel", default=None, help="plugin configuration name (default: autotune cache, then built-in choice)")
+    ap.add_argument("--kernel", default=None, help="plugin configuration name (default: autotune cache / heuristic pick, then a short trial)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the oracle check of sampled rows before the timed region")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N>1: fused = the epilogue stores into every rank's Y over NVLink (multimem stores to the NVSwitch multicast "
                          "address when the node offers one, else one TMA store per peer); nccl = all-gather + interleave kernel")
@@ -147,6 +218,7 @@ def main():
     import torch.distributed as dist
 
     import sm120_gemm_b200 as g
+    from sm120_gemm_b200.host_gemm import HostGemm, ShardedHostGemm
     from sm120_gemm_b200.shard import FusedNShardedGemm, NShardedGemm
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -168,47 +240,38 @@ def main():
         sys.exit("no kernel plugins found: run python -c 'import __graft_entry__ as e; e.build()'")
     cache = g.AutotuneCache()
     cache.load(os.path.join(ROOT, "sm120_gemm_b200", "autotune_cache.txt"))
-    # candidates: the autotune cache's pick for this (per-rank) shape and the built-in default;
-    # the faster of them over a few untimed launches is used (the reference also tunes before it times)
-    names = [args.kernel] if args.kernel else []
-    if not names:
-        hit = cache.lookup(M, N // world, K, "bf16", 1)
-        names = ([hit[0].name()] if hit else []) + DEFAULT_KERNELS
+    plan_rows = N // world
+    fused_wanted = world > 1 and args.gather == "fused"
+    # candidates: the dispatcher's pick for the per-rank shape (autotune cache entry, else the cost model) and one
+    # plugin of each large-tile family; the fastest over a few untimed launches is used (the reference also tunes
+    # before it times, src/bench.cu:304-477)
+    if args.kernel:
+        names = [args.kernel]
+    else:
+        pick = reg.select(cache, M, plan_rows, K, "bf16")
+        names = ([pick.config.name()] if pick else []) + ALTERNATE_FAMILY
     cands = []
     for n in dict.fromkeys(names):
         k = reg.find(n)
         if k is None:
             sys.exit(f"plugin {n} is not built")
-        if world > 1 and args.gather == "fused" and not args.kernel and (k.config.epi != 1 or k.config.split_k != 1):
+        if fused_wanted and not args.kernel and (k.config.epi != 1 or k.config.split_k != 1):
             continue        # the fused gather needs a TMA-store epilogue
         cands.append(k)
 
-    plan_rows = N // world
-    gen = torch.Generator(device=dev); gen.manual_seed(2)
-    X = torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16)
-    Wfull_seed = torch.Generator(device=dev); Wfull_seed.manual_seed(1002)
-    # every rank draws the same W stream and keeps its own rows (W never crosses GPUs)
-    W = torch.empty((plan_rows, K), dtype=torch.bfloat16, device=dev)
-    chunk = 2048
-    for r0 in range(0, N, chunk):
-        blk = torch.randn((chunk, K), device=dev, generator=Wfull_seed).to(torch.bfloat16)
-        lo, hi = max(r0, rank * plan_rows), min(r0 + chunk, (rank + 1) * plan_rows)
-        if lo < hi:
-            W[lo - rank * plan_rows:hi - rank * plan_rows] = blk[lo - r0:hi - r0]
-    del blk
+    X, W, w_blocks = make_inputs(torch, dev, rank, world)
     Y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     kern = cands[0]
-    fused_trial = world > 1 and args.gather == "fused" and all(k.config.epi == 1 and k.config.split_k == 1 for k in cands)
+    fused_trial = fused_wanted and all(k.config.epi == 1 and k.config.split_k == 1 for k in cands)
     if len(cands) > 1:
         # Untimed selection trial.  On several GPUs the candidates are tried as the whole fused step (GEMM with
-        # the gather in its epilogue, then the barrier): the tile whose GEMM alone is fastest can lose there,
-        # because its last wave holds more of the stores that nothing is left to hide.
+        # the gather in its epilogue, then the barrier).
         trial = []
         st = torch.cuda.current_stream().cuda_stream
         for k in cands:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             if fused_trial:
-                f = FusedNShardedGemm(k, M, N, K, rank, world)
+                f = FusedNShardedGemm(k, M, N, K, rank, world, double_buffer=False)
                 run_once = lambda: f.run(X, W)
             else:
                 ya = torch.empty((M, plan_rows), dtype=torch.bfloat16, device=dev)
@@ -231,17 +294,18 @@ def main():
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)      # every rank must make the same choice
         kern = cands[int(torch.argmin(t).item())]
-    fused = world > 1 and args.gather == "fused" and kern.config.epi == 1 and kern.config.split_k == 1
+    fused = fused_wanted and kern.config.epi == 1 and kern.config.split_k == 1
     if fused:
-        fop = FusedNShardedGemm(kern, M, N, K, rank, world)
-        Y = fop.Y
+        fop = FusedNShardedGemm(kern, M, N, K, rank, world)      # two symmetric result buffers used in turn
 
         class _Op:
             def run(self, X, W, Y):
                 return fop.run(X, W)
         op = _Op()
+        result = lambda: fop.Y
     else:
         op = NShardedGemm(kern, M, N, K, rank, world)
+        result = lambda: Y
 
     def barrier():
         if world > 1:
@@ -255,6 +319,13 @@ def main():
         launches_per_step += 1
     barrier()
     kern.check_status()
+
+    # never time a result that failed the check (the reference's rule, src/bench.cu:413-429)
+    check = None
+    if not args.no_check:
+        check = check_result(torch, dist, result(), X, w_blocks, rank, world)
+        if not check["ok"]:
+            sys.exit(f"rank {rank}: result check failed before timing: {check}")
 
     sampler = ClockSampler(local_rank); sampler.start()
     time.sleep(0.02)
@@ -278,36 +349,45 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
 
-    # ---- end to end: host buffers, copies inside the timed region (plugin C ABI in the middle)
+    # ---- end to end: host buffers in, host buffer out, copies inside the timed region, plugin C ABI in the middle.
+    # One GPU: X and W up, Y down.  N GPUs: every rank brings X and its weight rows up and takes its 1/N of the
+    # rows of Y down, so the job delivers one full Y to the host.  Both overlap copy-in, kernels and copy-out by
+    # row chunks on three streams.
+    slice_rows = M // world
     Xh = torch.empty((M, K), dtype=torch.bfloat16).pin_memory(); Xh.copy_(X)
     Wh = torch.empty((plan_rows, K), dtype=torch.bfloat16).pin_memory(); Wh.copy_(W)
-    Yh = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    Yh = torch.empty((slice_rows, N), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(2, min(args.steps, 5))
     if world == 1:
-        # one GPU: the package's host-buffer call, which overlaps copy-in, kernel and copy-out by row chunks
-        from sm120_gemm_b200.host_gemm import HostGemm
-
         hg = HostGemm(kern, M, N, K, chunk_rows=2048, device_X=X, device_W=W, device_Y=Y)
-
-        def e2e_step():
-            hg.run(Xh, Wh, Yh)
+        e2e_step = lambda: hg.run(Xh, Wh, Yh)
+        h2d, d2h = (M * K + N * K) * 2, M * N * 2
+    elif fused:
+        shg = ShardedHostGemm(fop, chunk_rows=2048, device_X=X, device_W=W)
+        e2e_step = lambda: shg.run(Xh, Wh, Yh)
+        h2d, d2h = shg.h2d_bytes, shg.d2h_bytes
     else:
+        r0 = rank * slice_rows
+
         def e2e_step():
             X.copy_(Xh, non_blocking=True)
             W.copy_(Wh, non_blocking=True)
             op.run(X, W, Y)
-            Yh.copy_(Y, non_blocking=True)
+            Yh.copy_(Y[r0:r0 + slice_rows], non_blocking=True)
+        h2d, d2h = (M * K + plan_rows * K) * 2, slice_rows * N * 2
 
     e2e_step(); barrier()
-    if world == 1 and rank == 0:
-        # the chunked host path must reproduce the device-resident result bit for bit
-        Ychk = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-        g.dispatch(kern, M, N, K, X.data_ptr(), W.data_ptr(), Ychk.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
-        torch.cuda.synchronize()
-        rows = torch.randint(0, M, (64,))
-        assert torch.equal(Yh[rows].cuda(), Ychk[rows.cuda()]), "host-buffer path differs from the resident path"
-        del Ychk
+    # the host-buffer path must reproduce the device-resident result bit for bit (sampled rows of this rank's slice)
+    Yres = result()
+    rows = torch.randint(0, slice_rows, (64,))
+    same = bool(torch.equal(Yh[rows].cuda(), Yres[(rows + rank * slice_rows).cuda()]))
+    if world > 1:
+        t = torch.tensor([1.0 if same else 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        same = bool(t.item() > 0.5)
+    assert same, "host-buffer path differs from the resident path"
     f0 = torch.cuda.Event(enable_timing=True); f1 = torch.cuda.Event(enable_timing=True)
+    barrier()
     f0.record()
     for _ in range(e2e_steps):
         e2e_step()
@@ -332,10 +412,13 @@ def main():
         roofline = {"bound": "tensor", "achieved": achieved if world == 1 else None, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": achieved / peaks["bf16_tflops"] if world == 1 else None, "traffic": NCU_TRAFFIC_BYTES.get(kern.config.name()) if world == 1 else None,
                     "peak_source": f"{peaks['source']} (cuBLAS bf16 burst; sustained {peaks['bf16_tflops_sustained']})",
+                    "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if world == 1 and peaks["bf16_tflops_sustained"] else None,
                     "kernel": f"umma_gemm_kernel<{kern.config.name()}>", "flops_per_launch": kflops, "avg_launch_ms": launch_ms}
+        clocks = sampler.result()
+        ms_per_step = total_ms / args.steps
         out = {
             "metric": "gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "kernel": kern.config.name(), "l2": "inputs larger than L2 (X, W, Y = 1.5 GiB vs 126 MB L2)",
                        "parallelism": "single GPU" if world == 1 else (
@@ -343,11 +426,16 @@ def main():
                            + ("(multimem stores to the NVSwitch multicast address of Y)" if fop.multicast else "(TMA stores to every rank's Y over NVLink)") + " + barrier"
                            if fused else f"N-sharded x{world}: {plan_rows} weight rows per rank + NCCL all-gather + interleave")},
             "roofline": roofline,
-            "e2e": {"value": flops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
-                    "h2d_bytes_per_step": (M * K + plan_rows * K) * 2, "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps},
+            "e2e": {"value": flops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+                    "h2d_bytes_per_rank": h2d, "d2h_bytes_per_rank": d2h, "steps": e2e_steps,
+                    "note": "pinned host X and weight rows in, one full Y back to the host (each rank returns its 1/N of the rows), chunked over three streams"},
             "gpu_launches": launches_per_step * args.steps,
-            "clocks": sampler.result(),
+            "clocks": clocks,
+            # step time in SM clock cycles (ms x median SM MHz under load x 1000): compares runs that ran at different clocks
+            "sm_clock_cycles_per_step": ms_per_step * clocks["sm_mhz"] * 1e3 if clocks.get("sm_mhz") else None,
         }
+        if check is not None:
+            out["check"] = check
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"], _ = cpu_baseline()
         print(json.dumps(out))

@@ -14,7 +14,7 @@ import ctypes
 import os
 from dataclasses import dataclass
 
-from .gen_configs import DT_IDS, GemmConfig, generate_configs
+from .gen_configs import DT_IDS, GemmConfig, generate_configs, heuristic_config, heuristic_ms
 
 KERNEL_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "kernels")
 
@@ -180,6 +180,17 @@ class KernelRegistry:
                 return k
         return None
 
+    def heuristic(self, M: int, N: int, K: int, dt: str = "bf16") -> LoadedKernel | None:
+        """The loaded plugin with the smallest modelled time for the shape (no measurement, no cache)."""
+        c = heuristic_config([k.config for k in self.kernels], dt, M, N, K)
+        return self.find(c.name()) if c else None
+
+    def select(self, cache: "AutotuneCache", M: int, N: int, K: int, dt: str = "bf16", gpus: int = 1) -> LoadedKernel | None:
+        """Dispatch without autotuning: the cache entry when there is one (and its plugin is loaded), else the heuristic pick."""
+        hit = cache.lookup(M, N, K, dt, gpus)
+        k = self.find(hit[0].name()) if hit else None
+        return k or self.heuristic(M, N, K, dt)
+
 
 class AutotuneCache:
     """Text cache ``dt,g,M,N,K name ms`` (reference format ``M,N,K name ms``, src/gemm_config.h:122-170;
@@ -284,5 +295,5 @@ def util_lib() -> ctypes.CDLL:
     return _UTIL
 
 
-__all__ = ["util_lib", "GemmConfig", "generate_configs", "KernelRegistry", "AutotuneCache", "LoadedKernel", "GemmArgs", "GemmError",
+__all__ = ["heuristic_config", "heuristic_ms", "GemmWeightFileInfo", "UTIL_SYMBOLS", "util_lib", "GemmConfig", "generate_configs", "KernelRegistry", "AutotuneCache", "LoadedKernel", "GemmArgs", "GemmError",
            "dispatch", "dispatch_ex", "load_plugin", "KERNEL_DIR", "ABI_SYMBOLS"]

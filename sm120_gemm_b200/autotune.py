@@ -29,7 +29,7 @@ SHAPES = [(512, 512, 14336), (1024, 1024, 14336), (1024, 1024, 1024), (2048, 204
 NOMINAL = {"bf16_tflops": 2250.0, "hbm_gbs": 8000.0}
 
 
-def time_fn(fn, stream, util, warmup=5, repeat=20, spacer_us=100):
+def time_fn(fn, stream, util, warmup=5, repeat=20, spacer_us=100000):
     import torch
 
     for _ in range(warmup):

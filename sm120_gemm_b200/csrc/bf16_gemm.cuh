@@ -611,7 +611,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     for (int i = 0; i < 16; i++) {
                         float x = v[i];
                         if (p.act == ACT_RELU) x = fmaxf(x, 0.f);
-                        else if (p.act == ACT_GELU) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+                        else if (p.act == ACT_GELU) x = 0.5f * x * erfcf(-x * 0.70710678118654752f);   // 1 + erf(t) = erfc(-t): no cancellation for x << 0
                         else if (p.act == ACT_SILU) x = x / (1.f + __expf(-x));
                         v[i] = x;
                         if (row_ok && col + i < p.N) tmax = fmaxf(tmax, fabsf(x));

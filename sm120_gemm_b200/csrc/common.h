@@ -18,11 +18,13 @@
         }                                                                                                 \
     } while (0)
 
-// idle spacer between timed launches (reference: sleep_kernel, src/common.h:16-19)
+// idle spacer between timed launches.  The reference launches sleep_kernel<<<1,1>>>(100), which asks __nanosleep for
+// 100 * 10^6 ns (src/common.h:16-19, 38); the hardware cuts one __nanosleep short at about a millisecond.  The default
+// here asks for the same 10^8 ns.
 static __global__ void sleep_kernel(uint32_t us) { __nanosleep(us * 1000u); }
 
 template <class F>
-double bench_ms(F &&launch, cudaStream_t stream, uint32_t warmup = 5, uint32_t repeat = 20, uint32_t spacer_us = 100)
+double bench_ms(F &&launch, cudaStream_t stream, uint32_t warmup = 5, uint32_t repeat = 20, uint32_t spacer_us = 100000)
 {
     for (uint32_t i = 0; i < warmup; i++) launch();
     CHECK_CUDA(cudaStreamSynchronize(stream));

@@ -15,6 +15,7 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <filesystem>
@@ -83,6 +84,12 @@ struct GemmConfig {
     // a plugin reports the exact figure through gemm_smem_bytes()).
     size_t smem_bytes() const
     {
+        if (dt == GEMM_DT_W4A16 && bk == 128) {   // tensor-memory family: load ring only (16 KB packed + 4 activation boxes per stage)
+            const size_t load_stage = 128 * 128 + 4 * (((size_t)bn * 128 + 1023) / 1024 * 1024);
+            const size_t fit = (200 * 1024) / load_stage;
+            const size_t load_stages = fit > 8 ? 8 : fit;
+            return load_stages * load_stage + (2 * load_stages + 3 * (size_t)num_stages) * 8 + 16 + 1024;
+        }
         if (dt == GEMM_DT_W4A16) {   // group ring (num_stages slots of two bf16 tiles) + load ring (16 KB packed + 4 activation boxes)
             const size_t load_stage = 128 * 128 + 4 * (((size_t)bn * 128 + 1023) / 1024 * 1024);
             const size_t fit = (224 * 1024 - (size_t)num_stages * 2 * 128 * 128) / load_stage;
@@ -112,6 +119,9 @@ struct LoadedKernel {
     int (*last_error)() = nullptr;
     const char *(*last_error_message)() = nullptr;
     int (*check_status)() = nullptr;
+    // bf16 split-K plugins: the GEMM with its partial sums in the plugin's built-in scratch array (no allocation
+    // anywhere); other plugins export the symbol too and answer GEMM_ERR_ARG
+    int (*run_no_alloc)(int M, int N, int K, const void *X, const void *W, void *Y, gemm_stream_t stream) = nullptr;
     void *dl_handle = nullptr;
 };
 
@@ -172,6 +182,7 @@ struct KernelRegistry {
             k.last_error = reinterpret_cast<int (*)()>(sym("gemm_last_error"));
             k.last_error_message = reinterpret_cast<const char *(*)()>(sym("gemm_last_error_message"));
             k.check_status = reinterpret_cast<int (*)()>(sym("gemm_check_status"));
+            k.run_no_alloc = reinterpret_cast<int (*)(int, int, int, const void *, const void *, void *, gemm_stream_t)>(sym("gemm_run_no_alloc"));
             auto name_fn = reinterpret_cast<const char *(*)()>(sym("gemm_config_name"));
             if (ok && cfg->name() != name_fn()) {
                 std::fprintf(stderr, "KernelRegistry: %s was built as %s\n", stem.c_str(), name_fn());
@@ -288,4 +299,72 @@ inline int dispatch(const LoadedKernel &kernel, int M, int N, int K, const void 
 {
     kernel.fn(M, N, K, X, W, Y, workspace, stream);
     return kernel.last_error();
+}
+
+// ---------------------------------------------------------------------------------- heuristic dispatch
+// A configuration for a shape that is not in the autotune cache, from a cost model instead of a measurement
+// (the reference has no such path: it prints "NO VALID CONFIG" or skips the shape, src/bench.cu:345-349, 455-458).
+// The model: the work is cut into tiles x split units dealt over the persistent grid in whole rounds; a unit costs
+// the larger of its tensor time (peak of the data type, derated for small tiles) and its streaming time (what one
+// SM can pull from memory), the whole launch cannot beat the algorithmic bytes over the HBM rate, and split-K pays
+// for its reduce kernel.  Only +,-,*,/ and ceil on doubles, so the Python mirror (gen_configs.heuristic_ms)
+// computes the same numbers; ties go to the name that sorts first.
+inline double heuristic_ms(const GemmConfig &c, int M, int N, int K, int sms = 148)
+{
+    static const double peak_tflops[5] = {2250.0, 4500.0, 4500.0, 2250.0, 9000.0};
+    const double hbm = 6.5e12, sm_stream = 9.0e10, launch_us = 4.0;
+    const double eb = sm100::elem_bits(c.dt) / 8.0;                         // bytes per operand element
+    const double wb = c.dt == GEMM_DT_W4A16 ? 0.5 : eb;
+    const double alg_bytes = (double)M * K * eb + (double)N * K * wb + (double)M * N * 2.0;
+    if (c.dt == GEMM_DT_W4A16)    // one kernel family: the narrowest padded M that fits, then the deeper ring
+        return alg_bytes / hbm * 1e3 + c.bn * 1e-4 - c.num_stages * 1e-6;
+    const double slots = (double)(sms / c.cg);
+    const double tiles = std::ceil((double)M / c.bm) * std::ceil((double)N / c.bn);
+    const double eff_m = c.bm >= 512 ? 1.0 : c.bm >= 256 ? 0.92 : 0.80;
+    const double eff_n = 0.55 + 0.45 * (c.bn < 256 ? c.bn : 256) / 256.0;
+    const double slot_flops = peak_tflops[c.dt] * 1e12 * c.cg / sms * eff_m * eff_n;
+    const double split = c.split_k > 1 ? c.split_k : 1;
+    const double unit_flops = 2.0 * c.bm * c.bn * (double)K / split;
+    const double unit_bytes = ((double)c.bm * eb + (double)c.bn * wb) * (double)K / split;
+    const double slot_bw = sm_stream * c.cg;
+    double t;
+    if (c.split_k == 0) {         // stream-K: every slot gets the same share
+        const double share = tiles / (tiles < slots ? tiles : slots);
+        const double tt = share * unit_flops / slot_flops, tm = share * unit_bytes / slot_bw;
+        t = (tt > tm ? tt : tm) * (tiles < slots ? tiles / slots : 1.0) + 4e-6;
+    } else {
+        const double rounds = std::ceil(tiles * split / slots);
+        const double tt = unit_flops / slot_flops, tm = unit_bytes / slot_bw;
+        t = rounds * (tt > tm ? tt : tm);
+        if (c.split_k > 1) t += (4.0 * split + 2.0) * M * N / 5.0e12 + 3e-6;
+    }
+    if (c.epi == 0 && M >= 1024) t *= 1.03;       // direct stores do not overlap the next tile as well as TMA stores
+    const double floor_t = alg_bytes / hbm;
+    if (t < floor_t) t = floor_t;
+    t -= c.num_stages * 1e-9;                      // between otherwise equal configurations, the deeper ring
+    return (t + launch_us * 1e-6) * 1e3;
+}
+
+// The loaded plugin of data type `dt` with the smallest modelled time for the shape (fused-transform plugins
+// are left out: they compute the same product and are asked for by name); nullptr when none can run it.
+inline const LoadedKernel *heuristic_kernel(const KernelRegistry &reg, int dt, int M, int N, int K, int sms = 148)
+{
+    const LoadedKernel *best = nullptr;
+    double best_ms = 0;
+    std::string best_name;
+    for (const auto &k : reg.kernels) {
+        if (k.config.dt != dt || k.config.epi == 2 || !k.can_run(M, N, K)) continue;
+        const double ms = heuristic_ms(k.config, M, N, K, sms);
+        const std::string name = k.config.name();
+        if (!best || ms < best_ms || (ms == best_ms && name < best_name)) { best = &k; best_ms = ms; best_name = name; }
+    }
+    return best;
+}
+
+// dispatch for callers that do not autotune: the cache entry when there is one, else the heuristic pick
+inline const LoadedKernel *select_kernel(const KernelRegistry &reg, const AutotuneCache &cache, int dt, int M, int N, int K, int gpus = 1)
+{
+    if (auto hit = cache.lookup(M, N, K, dt, gpus))
+        if (const LoadedKernel *k = reg.find(hit->config.name())) return k;
+    return heuristic_kernel(reg, dt, M, N, K);
 }

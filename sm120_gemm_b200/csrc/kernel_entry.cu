@@ -5,8 +5,10 @@
 // eight @VAR@ constants and one exported gemm_run); here the build passes
 //   -DGEMM_DT=<0..4> -DGEMM_BN=<64|128|192|256> -DGEMM_STAGES=<n> -DGEMM_CG=<1|2>
 //   -DGEMM_SK=<split-K> -DGEMM_AB=<0|1 operand swap> -DGEMM_EPI=<0|1|2> -DGEMM_MB=<1|2 row blocks per CTA>
+//   -DGEMM_BK=<K elements per pipeline unit>
 #include "bf16_gemm.cuh"
 #include "w4a16_gemm.cuh"
+#include "w4a16_tmem_gemm.cuh"
 
 #ifndef GEMM_DT
 #error "configuration macros missing: build through sm120_gemm_b200/build.py"
@@ -24,14 +26,22 @@ constexpr int EPI = GEMM_EPI;
 #ifndef GEMM_MB
 #define GEMM_MB 1
 #endif
+#ifndef GEMM_BK
+#define GEMM_BK 64
+#endif
 constexpr int MB = GEMM_MB;          // 128-row blocks of X per CTA
 constexpr int BM = 128 * CG * MB;
 
 #if GEMM_DT == 3
 // W4A16: operands swapped (AB = 1), BN is M padded, work is always cut stream-K fashion (SK = 0)
-static_assert(AB == 1 && SK == 0 && CG == 1 && EPI == 0, "W4A16 plugins are <dt>_bm128_bn<MPAD>_bk64_s<S>_cg1_sk0_ab1_e0");
+static_assert(AB == 1 && SK == 0 && CG == 1 && EPI == 0, "W4A16 plugins are <dt>_bm128_bn<MPAD>_bk<64|128>_s<S>_cg1_sk0_ab1_e0");
+#if GEMM_BK == 128   // dequantised weights through tensor memory
+using Traits = sm100::W4A16TmemTraits<BN, STAGES>;
+using Launcher = sm100::W4A16TmemLauncher<Traits>;
+#else                // dequantised weights through shared memory
 using Traits = sm100::W4A16Traits<BN, STAGES>;
 using Launcher = sm100::W4A16Launcher<Traits>;
+#endif
 #elif GEMM_DT == 0
 // BF16: through the reference's two entry-point classes, chosen at compile time exactly as its entry template
 // does (src/kernel_entry.cu.in:20-26): no split -> BF16GemmMMA, split-K (or stream-K) -> BF16GemmMMASplitK

@@ -10,6 +10,7 @@ shared-memory cap for the mma.sync kernel), re-derived for the tcgen05 design:
   bn       multiple of 16 up to 256  (UMMA N; two FP32 accumulator buffers need 2*bn <= 512 TMEM columns;
            the TMA-store epilogue needs a multiple of 64)
   bk       one 128-byte swizzle span of K per stage: 64 bf16, 128 fp8, 256 fp4 elements
+           (w4a16: 64 = dequantised tiles in shared memory, 128 = dequantised scale groups in tensor memory)
   s        TMA ring stages, bounded by the 227 KB of shared memory one CTA may use
   cg       CTA group (1 | 2)
   sk       split-K factor (FP32 partials + reduce kernel); 0 = stream-K: the tiles x k-blocks work is
@@ -69,6 +70,10 @@ class GemmConfig:
 
     def smem_bytes(self) -> int:
         """Dynamic shared memory of the kernel; must equal the traits' SMEM_ALLOC."""
+        if self.dt == "w4a16" and self.bk == 128:   # W4A16TmemTraits: load ring only (16 KB packed + 4 activation boxes per stage); s = group slots in TMEM
+            load_stage = 128 * 128 + 4 * (-(-self.bn * 128 // 1024) * 1024)
+            load_stages = min(8, 200 * 1024 // load_stage)
+            return load_stages * load_stage + (2 * load_stages + 3 * self.num_stages) * 8 + 16 + 1024
         if self.dt == "w4a16":   # W4A16Traits: group ring (s slots of two bf16 tiles) + load ring (16 KB packed + 4 activation boxes)
             load_stage = 128 * 128 + 4 * (-(-self.bn * 128 // 1024) * 1024)
             load_stages = min(4, (224 * 1024 - self.num_stages * 2 * 128 * 128) // load_stage)
@@ -103,7 +108,61 @@ class GemmConfig:
     def defines(self) -> list[str]:
         return [f"-DGEMM_DT={DT_IDS[self.dt]}", f"-DGEMM_BN={self.bn}", f"-DGEMM_STAGES={self.num_stages}",
                 f"-DGEMM_CG={self.cg}", f"-DGEMM_SK={self.split_k}", f"-DGEMM_AB={self.swap_ab}",
-                f"-DGEMM_EPI={self.epi}", f"-DGEMM_MB={self.mb}", f"-DGEMM_NAME={self.name()}"]
+                f"-DGEMM_EPI={self.epi}", f"-DGEMM_MB={self.mb}", f"-DGEMM_BK={self.bk}", f"-DGEMM_NAME={self.name()}"]
+
+
+_PEAK_TFLOPS = {"bf16": 2250.0, "fp8": 4500.0, "mxfp8": 4500.0, "w4a16": 2250.0, "w4a4": 9000.0}
+
+
+def heuristic_ms(c: GemmConfig, M: int, N: int, K: int, sms: int = 148) -> float:
+    """Modelled time of one launch, the same arithmetic as heuristic_ms in csrc/gemm_config.h (see there)."""
+    import math
+
+    hbm, sm_stream, launch_us = 6.5e12, 9.0e10, 4.0
+    eb = ELEM_BITS[c.dt] / 8.0
+    wb = 0.5 if c.dt == "w4a16" else eb
+    alg_bytes = float(M) * K * eb + float(N) * K * wb + float(M) * N * 2.0
+    if c.dt == "w4a16":
+        return alg_bytes / hbm * 1e3 + c.bn * 1e-4 - c.num_stages * 1e-6
+    slots = float(sms // c.cg)
+    tiles = math.ceil(M / c.bm) * float(math.ceil(N / c.bn))
+    eff_m = 1.0 if c.bm >= 512 else 0.92 if c.bm >= 256 else 0.80
+    eff_n = 0.55 + 0.45 * min(c.bn, 256) / 256.0
+    slot_flops = _PEAK_TFLOPS[c.dt] * 1e12 * c.cg / sms * eff_m * eff_n
+    split = float(c.split_k) if c.split_k > 1 else 1.0
+    unit_flops = 2.0 * c.bm * c.bn * float(K) / split
+    unit_bytes = (float(c.bm) * eb + float(c.bn) * wb) * float(K) / split
+    slot_bw = sm_stream * c.cg
+    if c.split_k == 0:
+        share = tiles / (tiles if tiles < slots else slots)
+        tt, tm = share * unit_flops / slot_flops, share * unit_bytes / slot_bw
+        t = (tt if tt > tm else tm) * (tiles / slots if tiles < slots else 1.0) + 4e-6
+    else:
+        rounds = float(math.ceil(tiles * split / slots))
+        tt, tm = unit_flops / slot_flops, unit_bytes / slot_bw
+        t = rounds * (tt if tt > tm else tm)
+        if c.split_k > 1:
+            t += (4.0 * split + 2.0) * M * N / 5.0e12 + 3e-6
+    if c.epi == 0 and M >= 1024:
+        t *= 1.03
+    floor_t = alg_bytes / hbm
+    if t < floor_t:
+        t = floor_t
+    t -= c.num_stages * 1e-9
+    return (t + launch_us * 1e-6) * 1e3
+
+
+def heuristic_config(configs, dt: str, M: int, N: int, K: int, sms: int = 148):
+    """The configuration of `configs` with the smallest modelled time for the shape, for callers that do not
+    autotune (the reference skips shapes that are missing from its cache, src/bench.cu:455-458)."""
+    best = None
+    for c in configs:
+        if c.dt != dt or c.epi == 2 or not c.is_valid_for(M, N, K):
+            continue
+        key = (heuristic_ms(c, M, N, K, sms), c.name())
+        if best is None or key < best[0]:
+            best = (key, c)
+    return best[1] if best else None
 
 
 def max_stages(dt: str, bn: int, cg: int, sk: int, epi: int, cap: int = MAX_SMEM) -> int:
@@ -130,9 +189,15 @@ def generate_block_scaled(dt: str, max_smem: int) -> list[GemmConfig]:
 
 
 def generate_w4a16(max_smem: int) -> list[GemmConfig]:
-    """W4A16 decode kernel: operands swapped (ab=1), bn = M padded to 16/32/64/128, stream-K work split."""
+    """W4A16 decode kernels: operands swapped (ab=1), bn = M padded to 16/32/64/128, stream-K work split.
+    bk128: dequantised weights go through tensor memory (A operand of the MMA read from TMEM), s = group slots;
+    bk64: dequantised weights go through shared memory, s = group ring slots."""
     out = []
-    for mpad, stage_opts in ((16, (3, 4)), (32, (3, 4)), (64, (3, 4)), (128, (2,))):
+    for mpad, slots in ((16, 6), (32, 5), (64, 4), (128, 2)):
+        c = GemmConfig("w4a16", 128, mpad, 128, slots, 1, 0, 1, 0)
+        if c.smem_bytes() <= max_smem:
+            out.append(c)
+    for mpad, stage_opts in ((16, (3, 4)), (32, (3, 4))):
         for st in stage_opts:
             c = GemmConfig("w4a16", 128, mpad, 64, st, 1, 0, 1, 0)
             if c.smem_bytes() <= max_smem:
@@ -191,7 +256,7 @@ def main() -> None:
     ap.add_argument("--max-smem-kb", type=int, default=MAX_SMEM // 1024)
     ap.add_argument("--dt", default="bf16,fp8,mxfp8,w4a4,w4a16")
     ap.add_argument("--output", default=None,
-                    help="write a CMake fragment  set(GEMM_CONFIGS \"name|DT|BN|STAGES|CG|SK|AB|EPI|MB;...\")  instead of printing names "
+                    help="write a CMake fragment  set(GEMM_CONFIGS \"name|DT|BN|STAGES|CG|SK|AB|EPI|MB|BK;...\")  instead of printing names "
                          "(the reference's generator does the same for its CMakeLists.txt, scripts/gen_configs.py:52-75)")
     args = ap.parse_args()
     configs = generate_configs(args.max_smem_kb * 1024, tuple(args.dt.split(",")))
@@ -199,7 +264,7 @@ def main() -> None:
         import os
 
         os.makedirs(os.path.dirname(os.path.abspath(args.output)), exist_ok=True)
-        items = [f"{c.name()}|{DT_IDS[c.dt]}|{c.bn}|{c.num_stages}|{c.cg}|{c.split_k}|{c.swap_ab}|{c.epi}|{c.mb}" for c in configs]
+        items = [f"{c.name()}|{DT_IDS[c.dt]}|{c.bn}|{c.num_stages}|{c.cg}|{c.split_k}|{c.swap_ab}|{c.epi}|{c.mb}|{c.bk}" for c in configs]
         with open(args.output, "w") as f:
             f.write("# generated by gen_configs.py -- one entry per kernel plugin\n")
             f.write('set(GEMM_CONFIGS "' + ";".join(items) + '")\n')

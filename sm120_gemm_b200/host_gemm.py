@@ -58,3 +58,69 @@ class HostGemm:
                 Yh[r0:r1].copy_(self.Y[r0:r1], non_blocking=True)
         cur.wait_stream(self.s_out)         # the caller's stream completes when the last rows are back on the host
         return launches
+
+
+class ShardedHostGemm:
+    """The same host-buffer call on the N-sharded path (one process per GPU): every rank brings the full X and
+    its own weight rows from pinned host memory, the row chunks run through the fused GEMM + all-gather
+    (``FusedNShardedGemm``: every rank's device Y receives every column block), and each rank returns only its
+    1/world slice of the ROWS of Y to the host, so the ranks together deliver one full Y (M*N*2 bytes in total,
+    not world times that).  Copy in, kernels and copy out overlap on three streams, chunk by chunk; a chunk is
+    copied out after the cross-rank barrier that follows its GEMM."""
+
+    def __init__(self, fused, chunk_rows: int = 2048, device_X=None, device_W=None):
+        import torch
+
+        self.torch = torch
+        self.f = fused
+        M, world = fused.M, fused.plan.world
+        if M % world != 0:
+            raise ValueError(f"M={M} rows do not split over {world} ranks")
+        self.slice_rows = M // world
+        self.row0 = fused.plan.rank * self.slice_rows
+        self.chunk = min(chunk_rows, self.slice_rows)
+        if self.slice_rows % self.chunk != 0:
+            raise ValueError(f"chunk of {self.chunk} rows does not divide the {self.slice_rows}-row slice of a rank")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.X = device_X if device_X is not None else torch.empty((M, fused.K), dtype=torch.bfloat16, device=dev)
+        self.W = device_W if device_W is not None else torch.empty((fused.plan.rows, fused.K), dtype=torch.bfloat16, device=dev)
+        self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        self.h2d_bytes = (M + fused.plan.rows) * fused.K * 2
+        self.d2h_bytes = self.slice_rows * fused.N * 2
+
+    def run(self, Xh, Wh_shard, Yh_slice) -> int:
+        """Xh: pinned M x K; Wh_shard: pinned (N/world) x K; Yh_slice: pinned (M/world) x N, receives rows
+        [rank*M/world, (rank+1)*M/world) of Y.  Returns the number of GEMM launches."""
+        from . import dispatch_ex
+
+        t, f = self.torch, self.f
+        cur = t.cuda.current_stream()
+        self.s_in.wait_stream(cur)
+        self.s_out.wait_stream(cur)
+        buf = f.step % len(f.buffers)
+        f.step += 1
+        Y, handle = f.buffers[buf], f.handles[buf]
+        if not f.double_buffer:
+            handle.barrier()
+        with t.cuda.stream(self.s_in):
+            self.W.copy_(Wh_shard, non_blocking=True)
+        launches = 0
+        for r0 in range(0, f.M, self.chunk):
+            r1 = r0 + self.chunk
+            with t.cuda.stream(self.s_in):
+                self.X[r0:r1].copy_(Xh[r0:r1], non_blocking=True)
+                landed = t.cuda.Event()
+                landed.record(self.s_in)
+            cur.wait_event(landed)
+            dispatch_ex(f.kernel, f._args(buf, r0, r1 - r0, self.X[r0:r1].data_ptr(), self.W.data_ptr(), cur.cuda_stream))
+            launches += 1
+            handle.barrier()                      # every rank's blocks of these rows have landed here
+            if self.row0 <= r0 < self.row0 + self.slice_rows:
+                done = t.cuda.Event()
+                done.record(cur)
+                self.s_out.wait_event(done)
+                with t.cuda.stream(self.s_out):
+                    Yh_slice[r0 - self.row0:r1 - self.row0].copy_(Y[r0:r1], non_blocking=True)
+        cur.wait_stream(self.s_out)
+        f.Y, f.handle = Y, handle
+        return launches

@@ -56,13 +56,21 @@ def destination_order(rank: int, world: int, rotate: bool = True, peers=None) ->
 
 class FusedNShardedGemm:
     """Per-rank GEMM whose epilogue stores its column block straight into the row-major Y of every
-    rank (TMA stores over NVLink into a symmetric buffer), so the all-gather overlaps the math tile by
-    tile and no interleave pass is needed.  ``run`` ends with a cross-rank barrier on the stream: after
-    it, this rank's Y holds every rank's block.  Needs a TMA-store configuration (``e1``, no split-K)."""
+    rank (TMA stores over NVLink into a symmetric buffer, or multimem stores to its NVSwitch multicast
+    address), so the all-gather overlaps the math tile by tile and no interleave pass is needed.
+    ``run`` ends with a cross-rank barrier on the stream: after it, this rank's ``Y`` holds every rank's
+    block.  Needs a TMA-store configuration (``e1``, no split-K).
 
-    def __init__(self, kernel, M: int, N: int, K: int, rank: int, world: int, group=None, rotate: bool = True, peers=None, multicast: bool = True):
-        import ctypes
+    Ordering between steps.  A step's stores land in the OTHER ranks' memory, so a rank that is quick out of
+    the barrier could start the next step and overwrite a result a slower rank is still reading.  With
+    ``double_buffer=True`` (default) two symmetric buffers are used in turn: step i+1 writes the buffer step i
+    did not use, and step i+2 can only begin after step i+1's barrier, which every rank reaches on its stream
+    after whatever it queued to read step i's result.  So a consumer that reads ``Y`` in stream order, before
+    it calls ``run`` again, is safe without a second barrier.  With ``double_buffer=False`` there is one buffer
+    and ``run`` opens with a barrier of its own instead (every rank is done with the previous result first)."""
 
+    def __init__(self, kernel, M: int, N: int, K: int, rank: int, world: int, group=None, rotate: bool = True, peers=None,
+                 multicast: bool = True, double_buffer: bool = True):
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
@@ -78,36 +86,56 @@ class FusedNShardedGemm:
         if not kernel.can_run(M, self.plan.rows, K):
             raise ValueError(f"{kernel.config.name()} cannot run the {M}x{self.plan.rows}x{K} shard")
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.Y = symm_mem.empty((M, N), dtype=torch.bfloat16, device=dev)       # same buffer on every rank
-        self.handle = symm_mem.rendezvous(self.Y, group if group is not None else dist.group.WORLD)
-        ptrs = list(self.handle.buffer_ptrs)
-        assert len(ptrs) == world <= 8
-        a = GemmArgs()
-        a.M, a.N, a.K = M, self.plan.rows, K
-        a.x_scale_f = a.w_scale_f = 1.0
+        self.double_buffer = bool(double_buffer)
+        self.buffers, self.handles, self.args_list = [], [], []
         # Destination order: own buffer first, then rank+1, rank+2, ... so that at any moment the ranks
         # (which walk their tiles in step) send to eight different GPUs instead of all to the same one.
         order = destination_order(rank, world, rotate, peers)
-        a.y_num_peers, a.y_col_offset, a.y_ld = len(order), self.plan.row_start, N
-        for i, r in enumerate(order):
-            a.y_peers[i] = ptrs[r]
-        # With an NVSwitch multicast mapping of the buffer one store reaches every rank, and each result byte
-        # leaves this GPU once instead of world-1 times; without one (or with fewer destinations than ranks)
-        # the epilogue stores to each peer in turn.
-        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
-        self.multicast = bool(multicast and mc and peers is None and self.plan.rows % 8 == 0
-                              and os.environ.get("SM100_GEMM_MULTICAST", "1") != "0")
-        a.y_multicast = mc if self.multicast else None
-        self.args = a
+        self.multicast = None
+        for _ in range(2 if self.double_buffer else 1):
+            Y = symm_mem.empty((M, N), dtype=torch.bfloat16, device=dev)       # same buffer on every rank
+            handle = symm_mem.rendezvous(Y, group if group is not None else dist.group.WORLD)
+            ptrs = list(handle.buffer_ptrs)
+            assert len(ptrs) == world <= 8
+            # With an NVSwitch multicast mapping of the buffer one store reaches every rank, and each result byte
+            # leaves this GPU once instead of world-1 times; without one (or with fewer destinations than ranks)
+            # the epilogue stores to each peer in turn.
+            mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+            use_mc = bool(multicast and mc and peers is None and self.plan.rows % 8 == 0 and os.environ.get("SM100_GEMM_MULTICAST", "1") != "0")
+            self.multicast = use_mc if self.multicast is None else (self.multicast and use_mc)
+            self.buffers.append(Y)
+            self.handles.append(handle)
+            self.args_list.append((ptrs, mc))
+        self.order = order
+        self.step = 0
+        self.Y = self.buffers[0]            # the buffer the most recent run() filled (the first one before any run)
+        self.handle = self.handles[0]
+        self._GemmArgs = GemmArgs
+
+    def _args(self, buf: int, row0: int, rows: int, X_ptr: int, W_ptr: int, stream: int):
+        """GemmArgs of one launch that computes Y rows [row0, row0 + rows) into buffer `buf` of every rank."""
+        ptrs, mc = self.args_list[buf]
+        a = self._GemmArgs()
+        a.M, a.N, a.K = rows, self.plan.rows, self.K
+        a.x_scale_f = a.w_scale_f = 1.0
+        a.y_num_peers, a.y_col_offset, a.y_ld = len(self.order), self.plan.row_start, self.N
+        off = row0 * self.N * 2
+        for i, r in enumerate(self.order):
+            a.y_peers[i] = ptrs[r] + off
+        a.y_multicast = (mc + off) if self.multicast else None
+        a.X, a.W, a.stream = X_ptr, W_ptr, stream
+        return a
 
     def run(self, X, W_shard):
         from . import dispatch_ex
 
-        a = self.args
-        a.X, a.W = X.data_ptr(), W_shard.data_ptr()
-        a.stream = self.torch.cuda.current_stream().cuda_stream
-        dispatch_ex(self.kernel, a)
-        self.handle.barrier()          # every rank's stores have landed before anyone reads Y
+        buf = self.step % len(self.buffers)
+        self.step += 1
+        if not self.double_buffer:
+            self.handles[buf].barrier()    # nobody still reads the previous result
+        dispatch_ex(self.kernel, self._args(buf, 0, self.M, X.data_ptr(), W_shard.data_ptr(), self.torch.cuda.current_stream().cuda_stream))
+        self.handles[buf].barrier()        # every rank's stores have landed before anyone reads Y
+        self.Y, self.handle = self.buffers[buf], self.handles[buf]
         return 1
 
 

@@ -4,6 +4,7 @@
 #include <cstdlib>
 #include <fstream>
 #include <set>
+#include <thread>
 
 #include "../sm120_gemm_b200/csrc/gemm_config.h"
 #include "../sm120_gemm_b200/csrc/tile_order.h"
@@ -116,6 +117,51 @@ int main(int argc, char **argv)
     CHECK(sm100::advance_desc_k(d, 3) - d == 6);
     const uint32_t i = sm100::make_idesc(sm100::UMMA_BF16, sm100::UMMA_BF16, 256, 192);
     CHECK(((i >> 4) & 3) == 1 && ((i >> 7) & 7) == 1 && ((i >> 10) & 7) == 1 && ((i >> 17) & 63) == 24 && ((i >> 24) & 31) == 16);
+
+    // with a plugin directory: the registry on real plugins, the heuristic dispatcher, two threads in the rejection paths
+    if (argc > 2) {
+        KernelRegistry reg;
+        reg.quiet = true;
+        CHECK(reg.load_dir(argv[2]) && reg.kernels.size() > 100);
+        const LoadedKernel *sk4 = reg.find("bf16_bm128_bn128_bk64_s7_cg1_sk4_ab0_e0");
+        const LoadedKernel *direct = reg.find("bf16_bm128_bn128_bk64_s6_cg1_sk1_ab0_e1");
+        CHECK(sk4 && direct && sk4->run_no_alloc && direct->run_no_alloc);
+        CHECK(sk4->run_no_alloc(2048, 2048, 1024, (void *)16, (void *)16, (void *)16, nullptr) == GEMM_ERR_WORKSPACE);   // 64 MiB of partials > 16 MiB
+        CHECK(direct->run_no_alloc(128, 128, 1024, (void *)16, (void *)16, (void *)16, nullptr) == GEMM_ERR_ARG);       // no scratch in this plugin
+        // one line per shape for the Python side to compare with its own model
+        static const int shapes[][4] = {{0, 1024, 1024, 1024}, {0, 128, 4096, 14336}, {0, 128, 28672, 4096}, {0, 8192, 8192, 8192}, {0, 16384, 2048, 16384},
+                                        {0, 512, 512, 14336}, {0, 1, 4096, 4096}, {0, 100, 136, 200}, {1, 8192, 8192, 8192}, {1, 128, 4096, 2048},
+                                        {2, 8192, 8192, 8192}, {2, 256, 512, 1024}, {4, 16, 28672, 8192}, {4, 8192, 8192, 8192}, {3, 16, 28672, 8192},
+                                        {3, 128, 28672, 8192}, {3, 1, 128, 128}};
+        for (const auto &sh : shapes) {
+            const LoadedKernel *k = heuristic_kernel(reg, sh[0], sh[1], sh[2], sh[3]);
+            CHECK(k && k->can_run(sh[1], sh[2], sh[3]) && k->config.dt == sh[0] && k->config.epi != 2);
+            std::printf("PICK %s %d %d %d %s\n", sm100::kDtypeNames[sh[0]], sh[1], sh[2], sh[3], k->config.name().c_str());
+        }
+        CHECK(heuristic_kernel(reg, GEMM_DT_BF16, 128, 130, 64) == nullptr);        // no plugin takes N % 8 != 0
+        AutotuneCache empty;
+        CHECK(select_kernel(reg, empty, GEMM_DT_BF16, 8192, 8192, 8192) == heuristic_kernel(reg, GEMM_DT_BF16, 8192, 8192, 8192));
+        empty.store(8192, 8192, 8192, direct->config, 1.0);
+        CHECK(select_kernel(reg, empty, GEMM_DT_BF16, 8192, 8192, 8192) == direct);
+        // the error state is per thread and the one-time set-up paths tolerate concurrent first calls
+        int codes[2] = {-1, -1};
+        auto worker = [&](int t) {
+            for (int i = 0; i < 200; i++) {
+                if (t == 0) {
+                    dispatch(*direct, 128, 130, 64, (void *)16, (void *)16, (void *)16, nullptr, nullptr);      // bad shape
+                    if (direct->last_error() != GEMM_ERR_SHAPE) return;
+                } else {
+                    if (sk4->run_no_alloc(2048, 2048, 1024, (void *)16, (void *)16, (void *)16, nullptr) != GEMM_ERR_WORKSPACE) return;
+                    if (sk4->last_error() != GEMM_ERR_WORKSPACE) return;
+                }
+            }
+            codes[t] = 0;
+        };
+        std::thread a(worker, 0), b(worker, 1);
+        a.join();
+        b.join();
+        CHECK(codes[0] == 0 && codes[1] == 0);
+    }
 
     std::printf("OK %d\n", checks);
     return 0;

@@ -25,6 +25,7 @@ def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel):
     import torch.distributed as dist
 
     import sm120_gemm_b200 as g
+    from sm120_gemm_b200.host_gemm import ShardedHostGemm
     from sm120_gemm_b200.shard import FusedNShardedGemm, NShardedGemm, shard_plan
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -42,15 +43,46 @@ def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel):
     g.dispatch(k, M, N, K, X.data_ptr(), W.data_ptr(), Yref.data_ptr(), 0, st)     # unsharded, this GPU alone
     plan = shard_plan(N, world, rank)
     Wr = W[plan.row_start:plan.row_start + plan.rows].contiguous()
-    fused = FusedNShardedGemm(k, M, N, K, rank, world, multicast=multicast)
-    fused.Y.fill_(float("nan"))
-    dist.barrier()
-    fused.run(X, Wr)
+    # a second, different problem for the step that follows immediately
+    X2 = torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16)
+    Yref2 = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    g.dispatch(k, M, N, K, X2.data_ptr(), W.data_ptr(), Yref2.data_ptr(), 0, st)
+    ok = []
+    for double_buffer in (True, False):
+        fused = FusedNShardedGemm(k, M, N, K, rank, world, multicast=multicast, double_buffer=double_buffer)
+        for b in fused.buffers:
+            b.fill_(float("nan"))
+        dist.barrier()
+        # two steps back to back with a read of the first result between them, in stream order and with no extra
+        # barrier: the second step's remote stores must not disturb what a slower rank is still reading
+        fused.run(X, Wr)
+        y1 = fused.Y.clone()
+        if rank == 0:
+            torch.cuda._sleep(20_000_000)          # rank 0 dawdles (about 10 ms) before its copy is queued behind the clone
+            y1b = fused.Y.clone()
+        else:
+            y1b = y1
+        fused.run(X2, Wr)
+        y2 = fused.Y.clone()
+        torch.cuda.synchronize()
+        ok += [bool(torch.equal(y1, Yref)), bool(torch.equal(y1b, Yref)), bool(torch.equal(y2, Yref2))]
+        used_multicast = bool(fused.multicast)
+        if double_buffer:
+            # host buffers in, this rank's slice of the rows of Y out, chunked over three streams
+            shg = ShardedHostGemm(fused, chunk_rows=M // world // 2)
+            Xh, Wh = X.cpu().pin_memory(), Wr.cpu().pin_memory()
+            Yh = torch.empty((M // world, N), dtype=torch.bfloat16).pin_memory()
+            shg.run(Xh, Wh, Yh)
+            torch.cuda.synchronize()
+            r0 = rank * (M // world)
+            ok.append(bool(torch.equal(Yh.cuda(), Yref[r0:r0 + M // world])))
+        dist.barrier()
+        del fused
     Yn = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
     NShardedGemm(k, M, N, K, rank, world).run(X, Wr, Yn)
     torch.cuda.synchronize()
     k.check_status()
-    ok = [bool(torch.equal(fused.Y, Yref)), bool(torch.equal(Yn, Yref)), bool(fused.multicast)]
+    ok += [bool(torch.equal(Yn, Yref)), used_multicast]
     np.save(os.path.join(out_dir, f"ok_{rank}.npy"), np.array(ok))
     dist.barrier()
     dist.destroy_process_group()
@@ -62,14 +94,16 @@ def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel):
 def test_two_gpu_sharded_equals_unsharded(tmp_path, multicast, kernel):
     import torch.multiprocessing as mp
 
-    world, M, N, K = 2, 1024 + 64, 2048, 1536       # M is not a tile multiple: the last row block is clipped
+    world, M, N, K = 2, 1024 + 64, 2048, 1536       # M is not a tile multiple: the last row block is clipped (272 rows per host chunk)
     mp.spawn(_worker, args=(world, _free_port(), M, N, K, str(tmp_path), multicast, kernel), nprocs=world, join=True)
     used = []
     for r in range(world):
         ok = np.load(tmp_path / f"ok_{r}.npy")
-        assert ok[0], f"rank {r}: fused-epilogue result differs from the unsharded one"
-        assert ok[1], f"rank {r}: NCCL all-gather result differs from the unsharded one"
-        used.append(bool(ok[2]))
+        names = ["two buffers: step 1", "two buffers: step 1 read late", "two buffers: step 2", "host-buffer sharded call",
+                 "one buffer: step 1", "one buffer: step 1 read late", "one buffer: step 2", "NCCL all-gather + interleave"]
+        for i, what in enumerate(names):
+            assert ok[i], f"rank {r}: {what} differs from the unsharded result"
+        used.append(bool(ok[len(names)]))
     if multicast and not all(used):
         pytest.skip("no multicast mapping of symmetric memory on this node: the peer-store path ran instead")
     assert all(used) == multicast

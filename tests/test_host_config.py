@@ -13,12 +13,40 @@ import sm120_gemm_b200 as g
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_cpp_header_checks(tmp_path):
+def test_cpp_header_checks(tmp_path, registry):
+    """The C++ header on its own (names, cache, scheduler arithmetic) and on the real plugins: every symbol
+    resolved (gemm_run_no_alloc included), the heuristic dispatcher, two threads in the rejection paths.
+    The heuristic picks must equal the Python mirror's."""
     exe = tmp_path / "host_config_test"
-    subprocess.check_call(["/usr/bin/g++", "-std=c++17", "-O1", "-I/usr/local/cuda/include", "-o", str(exe),
+    subprocess.check_call(["/usr/bin/g++", "-std=c++17", "-O1", "-pthread", "-I/usr/local/cuda/include", "-o", str(exe),
                            os.path.join(ROOT, "tests", "host_config_test.cpp"), "-ldl"])
-    out = subprocess.run([str(exe), str(tmp_path / "cache.txt")], capture_output=True, text=True)
-    assert out.returncode == 0 and out.stdout.strip().startswith("OK"), out.stdout + out.stderr
+    out = subprocess.run([str(exe), str(tmp_path / "cache.txt"), g.KERNEL_DIR], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.strip().splitlines()[-1].startswith("OK"), out.stdout + out.stderr
+    picks = [ln.split() for ln in out.stdout.splitlines() if ln.startswith("PICK")]
+    assert len(picks) >= 15
+    for _, dt, M, N, K, name in picks:
+        k = registry.heuristic(int(M), int(N), int(K), dt)
+        assert k is not None and k.config.name() == name, (dt, M, N, K, name, k and k.config.name())
+
+
+def test_heuristic_dispatch_needs_no_cache(registry):
+    """A shape missing from the autotune cache gets a runnable plugin from the cost model (the reference skips
+    such shapes, src/bench.cu:455-458); a cached shape keeps its entry."""
+    cache = g.AutotuneCache()
+    cache.load(os.path.join(ROOT, "sm120_gemm_b200", "autotune_cache.txt"))
+    for dt, shapes in {"bf16": [(1, 8, 8), (77, 1000, 4096), (3000, 5000, 7000 // 8 * 8), (128, 4096, 14336)],
+                       "fp8": [(64, 512, 1024), (8192, 8192, 8192)], "mxfp8": [(256, 512, 1024)], "w4a4": [(16, 28672, 8192)],
+                       "w4a16": [(1, 128, 128), (128, 28672, 8192)]}.items():
+        for (M, N, K) in shapes:
+            k = registry.select(cache, M, N, K, dt)
+            assert k is not None and k.config.dt == dt and k.can_run(M, N, K) and k.config.epi != 2
+            hit = cache.lookup(M, N, K, dt)
+            if hit:
+                assert k.config.name() == hit[0].name()
+    assert registry.heuristic(128, 130, 64) is None
+    # large square shapes go to the large CTA-pair tiles, one-row decode shapes to a split or stream-K plugin
+    assert registry.heuristic(8192, 8192, 8192).config.bm >= 256
+    assert registry.heuristic(16, 4096, 14336).config.split_k != 1
 
 
 def test_config_name_roundtrip_all_generated():
