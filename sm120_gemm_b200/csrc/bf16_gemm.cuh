@@ -204,19 +204,22 @@ struct UmmaGemmTraits {
     static constexpr int SF_BYTES = SF_A_BYTES + SF_B_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;   // bytes that arrive per stage
     static constexpr int OUT_CHUNK = 64;                   // output columns per TMA store (128 bytes of bf16)
-    // staging buffers of 128 rows x 64 bf16: two (one epilogue group: used in turn; two groups: one each), or
-    // four when two row blocks per CTA leave room (three ring stages): each group then has two in turn
-    static constexpr int STAGING_BUFS = (MB_ == 2 && STAGES_ <= 3) ? 4 : 2;
-    static constexpr int STAGING_BYTES = (EPI == EPI_TMA) ? STAGING_BUFS * EPI_ROWS * OUT_CHUNK * 2 : 0;
-    static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4;
-    static constexpr int SF_RING_BYTES = (STAGES_ * SF_BYTES + 1023) / 1024 * 1024;   // keeps the staging tiles 1024-byte aligned
-    static constexpr int SMEM_BYTES = STAGES_ * (A_BYTES + B_BYTES) + SF_RING_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + 16;
-    static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;   // slack to align the base to 1024 bytes
     static constexpr int ACC_STRIDE = (BN_ + 31) / 32 * 32;  // TMEM columns between the two accumulator buffers
     static constexpr int SF_COLS = SF_K_ATOMS * (1 + SF_N_ATOMS) * 4;   // TMEM columns of the staged scale factors
     // two FP32 accumulator buffers when they fit beside the scale factors, else one
     static constexpr int ACC_STAGE_COLS = MB_ * ACC_STRIDE;  // TMEM columns of one accumulator stage (MB_ row blocks side by side)
     static constexpr int ACC_STAGES = (2 * ACC_STAGE_COLS + SF_COLS <= 512) ? 2 : 1;
+    static constexpr int SF_RING_BYTES = (STAGES_ * SF_BYTES + 1023) / 1024 * 1024;   // keeps the staging tiles 1024-byte aligned
+    static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4;
+    static constexpr int RING_BYTES = STAGES_ * (A_BYTES + B_BYTES) + SF_RING_BYTES + NUM_BARRIERS * 8 + 16 + 1024;
+    // Staging buffers of 128 rows x 64 bf16.  Two by default (one epilogue group: used in turn; two groups: one each).
+    // A kernel with a single accumulator stage stalls its MMAs until the accumulator is drained, and with two
+    // buffers the drain waits for TMA stores to release them; where shared memory allows it such a kernel gets
+    // four, so each of its two epilogue groups drains its pieces back to back and hands the accumulator back at once.
+    static constexpr int STAGING_BUFS = (ACC_STAGES == 1 && RING_BYTES + 4 * EPI_ROWS * OUT_CHUNK * 2 <= 232448) ? 4 : 2;
+    static constexpr int STAGING_BYTES = (EPI == EPI_TMA) ? STAGING_BUFS * EPI_ROWS * OUT_CHUNK * 2 : 0;
+    static constexpr int SMEM_BYTES = STAGES_ * (A_BYTES + B_BYTES) + SF_RING_BYTES + STAGING_BYTES + NUM_BARRIERS * 8 + 16;
+    static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;   // slack to align the base to 1024 bytes
     static constexpr int ACC_COLS = ACC_STAGES * ACC_STAGE_COLS + SF_COLS;
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
     // Kernels with a single accumulator buffer cannot hide the epilogue behind the next main loop, so they

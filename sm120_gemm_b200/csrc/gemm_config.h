@@ -97,11 +97,17 @@ struct GemmConfig {
             return (size_t)num_stages * 2 * 128 * 128 + load_stages * load_stage + (2 * load_stages + 3 * (size_t)num_stages) * 8 + 16 + 1024;
         }
         const size_t k_atoms = (dt == GEMM_DT_MXFP8 || dt == GEMM_DT_W4A4) ? bk / 128 : 0;   // 512-byte scale atoms per stage
-        const size_t sf_ring = (num_stages * k_atoms * (1 + (bn + 127) / 128) * 512 + 1023) / 1024 * 1024;
-        const size_t a = (size_t)128 * 128 * (bm / (128 * cg) > 0 ? bm / (128 * cg) : 1), b = (size_t)(bn / cg) * 128;
-        const size_t staging = (split_k <= 1 && epi == 1) ? (size_t)((bm / (128 * cg) == 2 && num_stages <= 3) ? 4 : 2) * 128 * 64 * 2 : 0;
+        const size_t n_atoms = (bn + 127) / 128;
+        const size_t sf_ring = (num_stages * k_atoms * (1 + n_atoms) * 512 + 1023) / 1024 * 1024;
+        const size_t mb = bm / (128 * cg) > 0 ? bm / (128 * cg) : 1;
+        const size_t a = (size_t)128 * 128 * mb, b = (size_t)(bn / cg) * 128;
         const size_t barriers = (2 * (size_t)num_stages + 4) * 8 + 16;
-        return num_stages * (a + b) + sf_ring + staging + barriers + 1024;
+        const size_t ring = num_stages * (a + b) + sf_ring + barriers + 1024;
+        // a single accumulator stage (two do not fit in TMEM) gets four staging buffers when they fit
+        const bool one_acc_stage = 2 * mb * (((size_t)bn + 31) / 32 * 32) + k_atoms * (1 + n_atoms) * 4 > 512;
+        const size_t bufs = (one_acc_stage && ring + 4 * 128 * 64 * 2 <= 232448) ? 4 : 2;
+        const size_t staging = (split_k <= 1 && epi == 1) ? bufs * 128 * 64 * 2 : 0;
+        return ring + staging;
     }
 };
 

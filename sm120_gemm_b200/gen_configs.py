@@ -83,12 +83,17 @@ class GemmConfig:
         b = (self.bn // self.cg) * 128
         # block-scaled kinds stage one 512-byte scale atom per 128 rows and 128 K-elements
         k_atoms = self.bk // 128 if self.dt in ("mxfp8", "w4a4") else 0
-        sf = k_atoms * (1 + -(-self.bn // 128)) * 512
+        n_atoms = -(-self.bn // 128)
+        sf = k_atoms * (1 + n_atoms) * 512
         epi = 0 if self.split_k > 1 else self.epi
-        staging = (4 if self.mb == 2 and self.num_stages <= 3 else 2) * 128 * 64 * 2 if epi == 1 else 0
         barriers = (2 * self.num_stages + 4) * 8 + 16
         sf_ring = -(-self.num_stages * sf // 1024) * 1024
-        return self.num_stages * (a + b) + sf_ring + staging + barriers + 1024
+        ring = self.num_stages * (a + b) + sf_ring + barriers + 1024
+        # one accumulator stage (two do not fit in the 512 TMEM columns beside the scale factors): four staging buffers if they fit
+        acc_stages = 2 if 2 * self.mb * (-(-self.bn // 32) * 32) + k_atoms * (1 + n_atoms) * 4 <= 512 else 1
+        bufs = 4 if acc_stages == 1 and ring + 4 * 128 * 64 * 2 <= MAX_SMEM else 2
+        staging = bufs * 128 * 64 * 2 if epi == 1 else 0
+        return ring + staging
 
     def is_valid_for(self, M: int, N: int, K: int) -> bool:
         """The plugin's own gemm_can_run, restated (reference: src/gemm_config.h:34-38)."""
@@ -180,6 +185,9 @@ def generate_block_scaled(dt: str, max_smem: int) -> list[GemmConfig]:
     for bn in (128, 256):
         for epi in (1, 0):
             out.append(GemmConfig(dt, 256, bn, bk, min(max_stages(dt, bn, 2, 1, epi, max_smem), 8), 2, 1, 0, epi))
+    # 256 x 256 on a CTA pair has one accumulator stage: one ring stage fewer leaves room for four staging buffers,
+    # so the accumulator is drained without waiting for TMA stores
+    out.append(GemmConfig(dt, 256, 256, bk, 4, 2, 1, 0, 1))
     for bn in (128, 256):
         for epi in (1, 0):
             out.append(GemmConfig(dt, 128, bn, bk, min(max_stages(dt, bn, 1, 1, epi, max_smem), 8), 1, 1, 0, epi))

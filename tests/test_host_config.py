@@ -171,3 +171,22 @@ def test_bench_reference_arm_prints_the_contract_line():
     assert d["impl"] == "reference" and d["metric"] == "gemm_tflops" and d["unit"] == "TFLOPS" and d["value"] > 0
     assert d["higher_is_better"] is True and d["cpu_baseline"]["kind"] in ("port", "reference") and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"]["value"] == d["value"] and d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
+
+
+def test_cmake_build_configures_and_builds_a_plugin(tmp_path):
+    """The C++-only build (CMakeLists.txt at the repository root): configure for one data-type family, build one
+    plugin, the utility library and the host-side unit test, run it through ctest; the plugin must load and name
+    itself like its file."""
+    import shutil
+
+    if shutil.which("cmake") is None or shutil.which("ninja") is None:
+        pytest.skip("cmake / ninja not installed")
+    b = str(tmp_path / "build")
+    subprocess.check_call(["cmake", "-S", ROOT, "-B", b, "-G", "Ninja", "-DGEMM_DTYPES=w4a16", "-DCMAKE_CUDA_COMPILER=/usr/local/cuda/bin/nvcc",
+                           "-DCMAKE_CUDA_HOST_COMPILER=/usr/bin/g++"], stdout=subprocess.DEVNULL)
+    name = "w4a16_bm128_bn16_bk128_s6_cg1_sk0_ab1_e0"
+    subprocess.check_call(["cmake", "--build", b, "--target", f"gemm_{name}", "sm100gemm_util", "host_config_test"], stdout=subprocess.DEVNULL)
+    subprocess.check_call(["ctest", "--test-dir", b], stdout=subprocess.DEVNULL)
+    k = g.load_plugin(os.path.join(b, "kernels", f"libgemm_{name}.so"))
+    assert k.config.name() == name and k.can_run(16, 4096, 4096) and not k.can_run(17, 4096, 4096)
+    assert os.path.exists(os.path.join(b, "kernels", "libsm100gemm_util.so"))
