@@ -44,7 +44,7 @@ int gemm_quant_e4m3_per_tensor(const void *x, void *q, float *scale_out, float *
 int gemm_quant_mx(const void *x, void *q, void *sf_tiled, long long rows, int K, int kind, void *stream);
 
 /* bf16 w[rows][K] -> signed int4 (two per byte, low nibble = even k) + bf16 scales [rows][K/128]:
- * s = bf16(max|group| / 7) (1 for a zero group), q = clamp(rint(w / s), -8, 7).  K a multiple of 128. */
+ * s = bf16(max|group| / 7) (1 for a zero group), q = clamp(rint(w * (1 / s)), -8, 7).  K a multiple of 128. */
 int gemm_quant_int4_g128(const void *w, void *q, void *scales, long long rows, int K, void *stream);
 
 /* ---- offline weight packing and the weight file (host memory, host code).  No reference counterpart. */

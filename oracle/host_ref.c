@@ -372,7 +372,7 @@ void oracle_int4_dequantise(const uint8_t *packed, const uint16_t *scales, int N
 
 /*
  * Symmetric int4 quantisation of W4A16 weights, group-wise along K: s = bf16(max|w| / 7) (1 for an
- * all-zero group), q = clamp(rint(w / s), -8, 7), packed two per byte (low nibble = even k).
+ * all-zero group), q = clamp(rint(w * (1 / s)), -8, 7), packed two per byte (low nibble = even k).
  */
 void oracle_int4_quantise(const float *w, int N, int K, int group, uint8_t *packed, uint16_t *scales)
 {
@@ -385,9 +385,9 @@ void oracle_int4_quantise(const float *w, int N, int K, int group, uint8_t *pack
             for (int i = 0; i < group; i++) amax = fmaxf(amax, fabsf(p[i]));
             uint16_t sb = f32_to_bf16(amax > 0.f ? amax / 7.0f : 1.0f);
             scales[(size_t)n * G + g] = sb;
-            float s = bf16_to_f32(sb);
+            float inv = 1.0f / bf16_to_f32(sb);
             for (int i = 0; i < group; i += 2) {
-                float a = nearbyintf(p[i] / s), b = nearbyintf(p[i + 1] / s);
+                float a = nearbyintf(p[i] * inv), b = nearbyintf(p[i + 1] * inv);
                 a = fminf(fmaxf(a, -8.f), 7.f);
                 b = fminf(fmaxf(b, -8.f), 7.f);
                 packed[((size_t)n * K + (size_t)g * group + i) / 2] = (uint8_t)(((int)a & 0xf) | (((int)b & 0xf) << 4));

@@ -185,7 +185,7 @@ def int4_pack(q: np.ndarray) -> np.ndarray:
 
 
 def int4_quantise(w: np.ndarray, group: int = 128):
-    """float32 (N,K) -> (packed int4 (N,K/2), bf16 scale bits (N,K/group)): s = bf16(max|w|/7), q = clamp(rint(w/s))."""
+    """float32 (N,K) -> (packed int4 (N,K/2), bf16 scale bits (N,K/group)): s = bf16(max|w|/7), q = clamp(rint(w * (1/s)))."""
     w = np.ascontiguousarray(w, dtype=np.float32)
     N, K = w.shape
     assert K % group == 0

@@ -5,6 +5,7 @@
 //   bench --debug      fixed configurations called through the class templates, verbose checks
 // and one more for single measurements (profiling a kernel, sweeps):
 //   bench --kernel <config name> --shape M,N,K      time that one plugin
+//   bench --aux                                      the HBM-bound helper kernels alone (split-K reduce, quantisers, interleave) in GB/s
 // Options: --dtype bf16|fp8|mxfp8|w4a4|w4a16 (default bf16)   --dir <plugin dir>   --cache <file>
 //          --shape M,N,K (repeatable, replaces the built-in list)   --json <file> (one JSON object per line)
 //          --peaks <MEASURED_PEAKS.json> (adds "% of measured" beside the nominal roofline fractions)
@@ -397,6 +398,77 @@ double time_comparator(Problem &p, cublasHandle_t handle, cudaStream_t stream, s
     return ms;
 }
 
+// bench --aux: the HBM-bound helper kernels on their own, as GB/s of algorithmic bytes: the split-K reduce kernel
+// (decode-sized and large), the quantisation kernels and the column-block interleave.  Small cases rotate over
+// enough buffer sets to exceed twice the L2, like the GEMM timings.
+template <class F>
+void aux_line(const char *what, double bytes, F &&launch, cudaStream_t stream)
+{
+    const double ms = bench_ms(launch, stream);
+    const double gbs = bytes / ms / 1e6;
+    std::printf("  %-64s %9.4f ms  %8.0f GB/s  (%.1f%% of 8 TB/s", what, ms, gbs, 100.0 * gbs / kNominalHbmGbs);
+    if (g_measured_hbm_gbs > 0) std::printf(", %.1f%% of the measured %.0f GB/s copy rate", 100.0 * gbs / g_measured_hbm_gbs, g_measured_hbm_gbs);
+    std::printf(")\n");
+    if (g_json) { std::fprintf(g_json, "{\"mode\": \"aux\", \"kernel\": \"%s\", \"ms\": %.6g, \"algorithmic_gbs\": %.6g}\n", what, ms, gbs); std::fflush(g_json); }
+}
+
+template <int SK>
+void aux_reduce(const char *what, size_t M, size_t N, cudaStream_t stream)
+{
+    const size_t mn = M * N, per_set = mn * (4 * SK + 2);
+    int dev = 0, l2 = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev);
+    const int sets = (int)std::min<size_t>(16, std::max<size_t>(1, (2 * (size_t)l2 + per_set - 1) / per_set));
+    std::vector<std::unique_ptr<DevBuf<float>>> ws;
+    std::vector<std::unique_ptr<DevBuf<bf16>>> y;
+    for (int i = 0; i < sets; i++) {
+        ws.emplace_back(new DevBuf<float>(mn * SK));
+        y.emplace_back(new DevBuf<bf16>(mn));
+        if (!ws.back()->p || !y.back()->p) { std::printf("  %s: out of memory\n", what); return; }
+        cudaMemsetAsync(ws.back()->p, 0, mn * SK * 4, stream);
+    }
+    int next = 0;
+    size_t blocks = std::min<size_t>((mn / 8 + 255) / 256, (size_t)148 * 8);
+    aux_line(what, (double)per_set, [&] {
+        const int b = next++ % sets;
+        cudaLaunchConfig_t cfg = sm100::dependent_launch_config((unsigned)blocks, 256, stream);      // launched the way the plugins launch it
+        cudaLaunchKernelEx(&cfg, sm100::splitk_reduce_kernel<SK>, (const float *)ws[b]->p, y[b]->p, mn, 1.0f);
+    }, stream);
+}
+
+int aux_mode()
+{
+    cudaStream_t stream;
+    CHECK_CUDA(cudaStreamCreate(&stream));
+    std::printf("=== helper kernels: algorithmic bytes / device time ===\n");
+    aux_reduce<2>("splitk_reduce<2>  128 x 28672 (decode, 36.7 MB, rotating sets)", 128, 28672, stream);
+    aux_reduce<4>("splitk_reduce<4>  128 x 4096 (decode, 9.4 MB, rotating sets)", 128, 4096, stream);
+    aux_reduce<2>("splitk_reduce<2>  8192 x 8192 (671 MB)", 8192, 8192, stream);
+    aux_reduce<4>("splitk_reduce<4>  4096 x 8192 (604 MB)", 4096, 8192, stream);
+    const long long R = 8192, K = 8192;
+    DevBuf<bf16> x((size_t)R * K);
+    DevBuf<uint8_t> q((size_t)R * K), sf(gemm_mx_tiled_scale_bytes(R, (int)K)), sc(64);
+    DevBuf<bf16> gs((size_t)R * K / 128);
+    if (!x.p || !q.p || !sf.p || !sc.p || !gs.p) return 1;
+    {
+        std::vector<bf16> h((size_t)R * K);
+        srand(7);
+        fill_reference_random(h);
+        cudaMemcpy(x.p, h.data(), h.size() * 2, cudaMemcpyHostToDevice);
+    }
+    const double n = (double)R * K;
+    aux_line("gemm_quant_mx kind 8 (bf16 -> MXFP8)  8192 x 8192", n * (2 + 1 + 1.0 / 32), [&] { gemm_quant_mx(x.p, q.p, sf.p, R, (int)K, 8, stream); }, stream);
+    aux_line("gemm_quant_mx kind 4 (bf16 -> MX-FP4) 8192 x 8192", n * (2 + 0.5 + 1.0 / 32), [&] { gemm_quant_mx(x.p, q.p, sf.p, R, (int)K, 4, stream); }, stream);
+    aux_line("gemm_quant_e4m3_per_tensor (absmax + quantise) 8192 x 8192", n * (2 + 2 + 1),
+             [&] { gemm_quant_e4m3_per_tensor(x.p, q.p, reinterpret_cast<float *>(sc.p), reinterpret_cast<float *>(sc.p) + 1, R * K, stream); }, stream);
+    aux_line("gemm_quant_int4_g128 (bf16 -> int4 + group scales) 8192 x 8192", n * (2 + 0.5 + 2.0 / 128), [&] { gemm_quant_int4_g128(x.p, q.p, gs.p, R, (int)K, stream); }, stream);
+    DevBuf<bf16> blocked((size_t)R * K), y((size_t)R * K);
+    if (!blocked.p || !y.p) return 1;
+    aux_line("gemm_interleave_blocks 8 x [8192][1024] -> [8192][8192] bf16", n * 4, [&] { gemm_interleave_blocks(blocked.p, y.p, 8, R, (int)K / 8, 2, stream); }, stream);
+    return 0;
+}
+
 struct Options {
     std::string mode, dir, cache = "autotune_cache.txt", kernel, host_ref;
     int dt = GEMM_DT_BF16;
@@ -632,7 +704,7 @@ int main(int argc, char **argv)
     std::vector<Shape> shapes;
     for (int i = 1; i < argc; i++) {
         const std::string a = argv[i];
-        if (a == "--debug" || a == "--autotune") o.mode = a;
+        if (a == "--debug" || a == "--autotune" || a == "--aux") o.mode = a;
         else if (a == "--dir" && i + 1 < argc) o.dir = argv[++i];
         else if (a == "--cache" && i + 1 < argc) o.cache = argv[++i];
         else if (a == "--kernel" && i + 1 < argc) o.kernel = argv[++i];
@@ -649,7 +721,7 @@ int main(int argc, char **argv)
             if (std::sscanf(argv[++i], "%d,%d,%d", &s.M, &s.N, &s.K) != 3) { std::fprintf(stderr, "bad --shape\n"); return 2; }
             shapes.push_back(s);
         } else {
-            std::fprintf(stderr, "usage: bench [--debug | --autotune] [--dtype bf16|fp8|mxfp8|w4a4|w4a16] [--dir D] [--cache F] [--shape M,N,K]...\n"
+            std::fprintf(stderr, "usage: bench [--debug | --autotune | --aux] [--dtype bf16|fp8|mxfp8|w4a4|w4a16] [--dir D] [--cache F] [--shape M,N,K]...\n"
                                  "             [--kernel NAME] [--json FILE] [--peaks MEASURED_PEAKS.json] [--host-ref liboracle.so]\n");
             return 2;
         }
@@ -665,7 +737,8 @@ int main(int argc, char **argv)
     }
     if (!o.host_ref.empty()) host_reference_line(o.host_ref);
     int rc;
-    if (o.mode == "--debug") rc = debug_mode();
+    if (o.mode == "--aux") rc = aux_mode();
+    else if (o.mode == "--debug") rc = debug_mode();
     else if (o.mode == "--autotune") rc = autotune(o);
     else rc = quick(o);
     if (g_json) std::fclose(g_json);

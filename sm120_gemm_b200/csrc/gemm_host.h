@@ -171,6 +171,48 @@ inline int make_tmap_2d(CUtensorMap *out, CUtensorMapDataType dtype, const void 
     return GEMM_OK;
 }
 
+// Row-major 2-D tensor seen as 3-D so that ONE copy brings several 128-byte column chunks of the same rows:
+// dimension 0 = the `chunk_elems` elements of a chunk, dimension 1 = rows (pitch bytes apart), dimension 2 = chunks
+// along the row (chunk bytes apart).  A box of (chunk_elems, box_rows, box_chunks) lands in shared memory as
+// box_chunks consecutive [box_rows][chunk] tiles, each in the canonical 128-byte-swizzled K-major form the MMA
+// descriptors expect -- what box_chunks separate 2-D copies would have produced, for one TMA request.
+inline int make_tmap_chunked(CUtensorMap *out, CUtensorMapDataType dtype, int elem_bytes, const void *ptr, uint64_t row_elems, uint64_t rows,
+                             uint64_t pitch_bytes, uint32_t chunk_elems, uint32_t box_rows, uint32_t box_chunks)
+{
+    struct Slot {
+        const void *ptr;
+        uint64_t row_elems, rows, pitch;
+        uint32_t chunk, box_rows, box_chunks;
+        int dtype;
+        CUtensorMap map;
+        bool used;
+    };
+    static thread_local Slot cache[8];
+    static thread_local unsigned next = 0;
+    for (auto &c : cache)
+        if (c.used && c.ptr == ptr && c.row_elems == row_elems && c.rows == rows && c.pitch == pitch_bytes && c.chunk == chunk_elems &&
+            c.box_rows == box_rows && c.box_chunks == box_chunks && c.dtype == (int)dtype) {
+            *out = c.map;
+            return GEMM_OK;
+        }
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return set_error(GEMM_ERR_DRIVER, "cuTensorMapEncodeTiled entry point not available");
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0 || (pitch_bytes & 15u) != 0)
+        return set_error(GEMM_ERR_ARG, "tensor base %p / pitch %llu bytes must be 16-byte aligned", ptr, (unsigned long long)pitch_bytes);
+    cuuint64_t dims[3] = {chunk_elems, rows, (row_elems + chunk_elems - 1) / chunk_elems};
+    cuuint64_t strides[2] = {pitch_bytes, (cuuint64_t)chunk_elems * elem_bytes};
+    cuuint32_t box[3] = {chunk_elems, box_rows, box_chunks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, dtype, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return set_error(GEMM_ERR_DRIVER, "cuTensorMapEncodeTiled (chunked view) failed (%d) row=%llu rows=%llu box=%ux%ux%u", (int)r,
+                         (unsigned long long)row_elems, (unsigned long long)rows, chunk_elems, box_rows, box_chunks);
+    Slot &c = cache[next++ % 8];
+    c = Slot{ptr, row_elems, rows, pitch_bytes, chunk_elems, box_rows, box_chunks, (int)dtype, *out, true};
+    return GEMM_OK;
+}
+
 // Reads and clears the device status block of the current device (synchronises the device).
 inline int read_device_status(uint32_t out[4])
 {

@@ -13,7 +13,7 @@
 //   per-tensor:  scale = amax / 448;  q = e4m3_rne_sat(x * (1 / scale))
 //   MX block:    sc = clamp(ceil(log2(amax / emax)) + 127, 0, 254) (127 for an all-zero block);
 //                q = cvt(x * 2^(127 - sc)),  emax = 448 (e4m3) or 6 (e2m1)
-//   int4 group:  s = bf16(amax / 7) (1 for an all-zero group);  q = clamp(rint(x / s), -8, 7)
+//   int4 group:  s = bf16(amax / 7) (1 for an all-zero group);  q = clamp(rint(x * (1 / s)), -8, 7)
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -39,25 +39,33 @@ __device__ __forceinline__ uint32_t e4m3x2(float a, float b)
     return r;
 }
 
-// float -> e2m1 code (sign in bit 3): nearest of {0, .5, 1, 1.5, 2, 3, 4, 6}, ties to the even code, saturating
-__device__ __forceinline__ uint32_t e2m1(float x)
+// two floats -> two e2m1 codes in one byte (`a` in the low nibble): round to nearest, ties to the even code, saturating
+__device__ __forceinline__ uint32_t e2m1x2(float a, float b)
 {
-    const float a = fabsf(x);
-    uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
-    if (a != a) c = 7;
-    return c | ((__float_as_uint(x) >> 28) & 8u);
+    uint16_t r;
+    asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}" : "=h"(r) : "f"(b), "f"(a));
+    return r;
 }
 
-// ue8m0 code of the smallest power of two >= amax / emax
-__device__ __forceinline__ uint32_t ue8m0_for_block(float amax, float emax)
+// ue8m0 code of the smallest power of two >= amax / emax, for an amax that is a bf16 value (as every |x| here is) and
+// emax = (1 + FRAC128 / 128) * 2^EMAX_EXP (448 = 1.75 * 2^8, 6 = 1.5 * 2^2).  With amax = (1 + m/128) * 2^e the quotient
+// is at most 2^(e - EMAX_EXP) when m <= FRAC128 and above it otherwise, so the answer is a matter of the exponent field
+// and one comparison of the 7 mantissa bits -- no division, frexp or ldexp.  (A bf16 mantissa step is 1/128, far
+// coarser than the rounding of the FP32 division the host definition performs, so the two agree bit for bit.)
+template <int EMAX_EXP, int FRAC128>
+__device__ __forceinline__ uint32_t ue8m0_for_block(float amax)
 {
-    if (!(amax > 0.f)) return 127u;
-    const float t = amax / emax;
-    int e;
-    const float m = frexpf(t, &e);
-    int p = (m == 0.5f ? e - 1 : e) + 127;
-    p = p < 0 ? 0 : (p > 254 ? 254 : p);
-    return (uint32_t)p;
+    const uint32_t bits = __float_as_uint(amax) >> 16;          // bf16 bit pattern, sign clear
+    if (bits == 0) return 127u;                                 // all-zero block: scale 1
+    int p = (int)(bits >> 7) - EMAX_EXP + ((int)(bits & 127u) > FRAC128 ? 1 : 0);
+    if ((bits >> 7) == 0) p = 0;                                // bf16 subnormal maximum: far below the smallest scale
+    return (uint32_t)(p < 0 ? 0 : (p > 254 ? 254 : p));
+}
+
+// 2^(127 - sc) as a float (sc = 254 gives the subnormal 2^-127)
+__device__ __forceinline__ float inv_scale_of(uint32_t sc)
+{
+    return __uint_as_float(sc >= 254u ? 0x00400000u : (254u - sc) << 23);
 }
 
 // byte offset of the scale of (row r, K-block kb) in the atom layout
@@ -123,7 +131,6 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const uint4 *__restrict__
 {
     const int vec_per_row = K / 8;                        // 16-byte pieces per row (K is a multiple of 128)
     const long long total = rows_padded * vec_per_row;
-    const float emax = FP4 ? 6.0f : 448.0f;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / vec_per_row;
         const int v = (int)(i - r * vec_per_row);
@@ -140,18 +147,17 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const uint4 *__restrict__
         }
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-        const uint32_t sc = ue8m0_for_block(m, emax);
+        const uint32_t sc = FP4 ? ue8m0_for_block<2, 64>(m) : ue8m0_for_block<8, 96>(m);
         // the four scale bytes of this 128-element span, collected in the span's first lane
         const int base = lane & 16;
         uint32_t word = __shfl_sync(0xffffffffu, sc, base) | (__shfl_sync(0xffffffffu, sc, base + 4) << 8) |
                         (__shfl_sync(0xffffffffu, sc, base + 8) << 16) | (__shfl_sync(0xffffffffu, sc, base + 12) << 24);
         if ((lane & 15) == 0) *reinterpret_cast<uint32_t *>(sf + sf_tiled_offset(r, v / 4, k_atoms)) = word;
         if (r >= rows) continue;
-        const float inv = ldexpf(1.0f, 127 - (int)sc);
+        const float inv = inv_scale_of(sc);
         if (FP4) {
-            uint32_t o = 0;
-#pragma unroll
-            for (int j = 0; j < 8; j++) o |= e2m1(f[j] * inv) << (4 * j);
+            const uint32_t o = e2m1x2(f[0] * inv, f[1] * inv) | (e2m1x2(f[2] * inv, f[3] * inv) << 8) | (e2m1x2(f[4] * inv, f[5] * inv) << 16) |
+                               (e2m1x2(f[6] * inv, f[7] * inv) << 24);
             static_cast<uint32_t *>(q)[i] = o;
         } else {
             uint2 o;
@@ -178,11 +184,11 @@ __global__ void __launch_bounds__(256) quant_int4_kernel(const uint4 *__restrict
 #pragma unroll
         for (int o = 1; o < 16; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         const __nv_bfloat16 sb = __float2bfloat16_rn(m > 0.f ? m / 7.0f : 1.0f);
-        const float s = __bfloat162float(sb);
+        const float inv = 1.0f / __bfloat162float(sb);
         uint32_t o = 0;
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            float t = rintf(f[j] / s);
+            float t = rintf(f[j] * inv);
             t = fminf(fmaxf(t, -8.f), 7.f);
             o |= ((uint32_t)(int)t & 0xfu) << (4 * j);
         }
@@ -253,7 +259,7 @@ int gemm_quant_mx(const void *x, void *q, void *sf_tiled, long long rows, int K,
 }
 
 // bf16 w[rows][K] -> signed int4, two per byte (low nibble = even k), and one bf16 scale per 128 K-elements
-// ([rows][K/128]): s = bf16(max|w| / 7), q = clamp(rint(w / s), -8, 7).  K a multiple of 128.
+// ([rows][K/128]): s = bf16(max|w| / 7), q = clamp(rint(w * (1 / s)), -8, 7).  K a multiple of 128.
 int gemm_quant_int4_g128(const void *w, void *q, void *scales, long long rows, int K, void *stream)
 {
     if (rows <= 0 || K <= 0 || K % 128 != 0 || !w || !q || !scales || !aligned16(w) || (reinterpret_cast<uintptr_t>(q) & 3u)) return (int)cudaErrorInvalidValue;

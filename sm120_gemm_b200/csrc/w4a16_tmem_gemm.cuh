@@ -11,12 +11,15 @@
 // group into its own accumulator, FP32 fold  total[m] += s[n][g] * acc[m]), same operand swap (128 weight
 // rows = TMEM lanes, UMMA N = M padded), same stream-K work split and fix-up kernel.
 //
+// The SM's instruction issue is the scarce resource here (the int4 -> bf16 conversion alone is ~1300 warp
+// instructions per group), so every wait backs off with nanosleep instead of polling back to back: a polling
+// warp takes issue slots from the dequantisers that share its scheduler.
 // Warps:  0 TMA producer | 1 MMA issuer | 2 TMEM alloc | 3 idle
 //         4 .. 4+4*FOLD-1   fold + epilogue: thread r of a group owns weight row r (TMEM lane r) and the group's
 //                           share of the M columns
-//         then TEAMS x 4    dequantiser teams: thread r converts row r of a whole scale group (64 packed bytes ->
-//                           64 registers of bf16 pairs -> one tcgen05.st into the group slot's A columns);
-//                           teams take groups in turn
+//         then TEAMS x 4    dequantiser teams: thread r converts row r of HALF a scale group (32 packed bytes ->
+//                           32 registers of bf16 pairs -> one tcgen05.st into half of the group slot's A columns);
+//                           teams take the half-groups in turn
 // TMEM columns: SLOTS accumulators of MPAD columns, then SLOTS A buffers of 64 columns (128 bf16 per lane).
 // LOAD ring, stages of 256 K-elements (two groups): one TMA box of 128 rows x 128 packed bytes plus the four
 // 64-element activation boxes of the same K range.
@@ -32,21 +35,16 @@
 
 namespace sm100 {
 
-// 32 lanes x 64 consecutive 32-bit columns, registers -> TMEM: thread t of the warp writes lane (base_lane + t)
-__device__ __forceinline__ void tmem_st_32x64(uint32_t taddr, const uint32_t (&r)[64])
+// 32 lanes x 32 consecutive 32-bit columns, registers -> TMEM: thread t of the warp writes lane (base_lane + t)
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32])
 {
     asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x64.b32 [%0], "
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, "
-        "%33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, "
-        "%49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63, %64};"
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
           "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
-          "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(r[32]),
-          "r"(r[33]), "r"(r[34]), "r"(r[35]), "r"(r[36]), "r"(r[37]), "r"(r[38]), "r"(r[39]), "r"(r[40]), "r"(r[41]), "r"(r[42]), "r"(r[43]),
-          "r"(r[44]), "r"(r[45]), "r"(r[46]), "r"(r[47]), "r"(r[48]), "r"(r[49]), "r"(r[50]), "r"(r[51]), "r"(r[52]), "r"(r[53]), "r"(r[54]),
-          "r"(r[55]), "r"(r[56]), "r"(r[57]), "r"(r[58]), "r"(r[59]), "r"(r[60]), "r"(r[61]), "r"(r[62]), "r"(r[63])
+          "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
 
@@ -74,7 +72,8 @@ struct W4A16TmemTraits {
     static constexpr int LOAD_KB = 4;                  // 64-element activation boxes per load stage
     static constexpr int PACKED_BYTES = TILE_N * 128;  // 16 KB of int4 per load stage
     static constexpr int X_BYTES = MPAD_ * 128;        // one activation box
-    static constexpr int X_STRIDE = (X_BYTES + 1023) / 1024 * 1024;
+    static constexpr int X_STRIDE = X_BYTES;           // the boxes of a stage are contiguous (one request brings all four)
+    static_assert(X_BYTES % 1024 == 0, "an activation box is a whole number of 8-row swizzle groups");
     static constexpr int LOAD_STAGE_SMEM = PACKED_BYTES + LOAD_KB * X_STRIDE;
     static constexpr int LOAD_TX_BYTES = PACKED_BYTES + LOAD_KB * X_BYTES;
     static constexpr int LOAD_STAGES_FIT = (200 * 1024) / LOAD_STAGE_SMEM;
@@ -88,11 +87,21 @@ struct W4A16TmemTraits {
     static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
     static constexpr int FOLD = MPAD_ > 64 ? 2 : 1;    // fold groups: each keeps MPAD / FOLD running totals per thread
     static constexpr int FCOLS = MPAD_ / FOLD;
-    static constexpr int TEAMS = MPAD_ > 64 ? 1 : 2;   // dequantiser teams (M = 128 is bound by its MMAs, and two fold groups need the registers)
+    // dequantiser teams of four warps; the unit of work is HALF a scale group (64 K-elements of 128 rows: 32 registers
+    // per thread), dealt to the teams in turn.  A single warp sustains well under one instruction per clock on the
+    // dependent prmt / lop3 / sub chains of the conversion, so the way to more conversion throughput is more warps.
+    static constexpr int TEAMS = MPAD_ > 64 ? 2 : MPAD_ > 32 ? 3 : 4;   // fewer where the fold warps need the registers
     static constexpr int THREADS = 128 + 128 * FOLD + 128 * TEAMS;
     static constexpr int REGS_EVEN = 65536 / THREADS / 8 * 8;                      // what the launch bound gives every thread
-    static constexpr int FOLD_REGS_FIT = (65536 - 128 * 56 - 128 * TEAMS * REGS_EVEN) / (128 * FOLD) / 8 * 8;
+    static constexpr int LEAN_REGS = 40;                                           // setmaxnreg target of warps 0-3
+    static constexpr int DEQ_REGS = REGS_EVEN < 80 ? REGS_EVEN : 80;               // and of the dequantiser warps (32 output registers each)
+    // setmaxnreg moves registers inside the CTA's own allocation (THREADS x REGS_EVEN), not the SM's whole file: an
+    // increase that the decreases of the other roles do not cover would wait for ever
+    static constexpr int POOL = THREADS * REGS_EVEN;
+    static constexpr int FOLD_REGS_FIT = (POOL - 128 * LEAN_REGS - 128 * TEAMS * DEQ_REGS) / (128 * FOLD) / 8 * 8;
     static constexpr int FOLD_REGS = FOLD_REGS_FIT > 168 ? 168 : FOLD_REGS_FIT;    // setmaxnreg target of the fold warps
+    static_assert(128 * LEAN_REGS + 128 * TEAMS * DEQ_REGS + 128 * FOLD * FOLD_REGS <= POOL && FOLD_REGS >= REGS_EVEN,
+                  "the roles' register targets must fit in what the CTA was launched with");
     static_assert(MPAD_ == 16 || MPAD_ == 32 || MPAD_ == 64 || MPAD_ == 128, "padded M is 16, 32, 64 or 128");
     static_assert(SLOTS_ >= 2 && TMEM_USED <= 512, "2 or more group slots that fit in TMEM");
     static_assert(LOAD_STAGES >= 2, "at least two load stages must fit");
@@ -131,7 +140,7 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             mbar_init(lfree_bar(s), 2);              // one commit per group of the stage (a lone group commits twice)
         }
         for (int s = 0; s < SLOTS; s++) {
-            mbar_init(ready_bar(s), 4);              // one arrival per warp of the team that converted the group
+            mbar_init(ready_bar(s), 8);              // one arrival per warp of the two teams that converted the group's halves
             mbar_init(gdone_bar(s), 1);
             mbar_init(gempty_bar(s), 4 * T::FOLD);   // one arrival per fold warp
         }
@@ -161,7 +170,7 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     // (MPAD / FOLD running totals per thread) take more than the even share.  Warps 0-3, each fold group and each
     // dequantiser team are whole warpgroups, as setmaxnreg wants.
     if (warp < 4) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(T::LEAN_REGS));
       if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -173,7 +182,7 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 const int n0 = w.tile * T::TILE_N;
                 for (int g = 0; g < w.kb_count; g += T::LOAD_GROUPS, pcount++) {
                     const int ps = pcount % LSTAGES;
-                    if (!mbar_wait(lfree_bar(ps), (((uint32_t)(pcount / LSTAGES)) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, ps)) {
+                    if (!mbar_wait(lfree_bar(ps), (((uint32_t)(pcount / LSTAGES)) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_PRODUCER, ps, 256)) {
                         ok = false;
                         break;
                     }
@@ -182,9 +191,8 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                     // always the full 256-element box: past an item's end it brings unused (or zero-filled) data
                     mbar_arrive_expect_tx(landed_bar(ps), T::LOAD_TX_BYTES);
                     tma_load_2d(dst, &tmap_w, landed_bar(ps), k0 / 2, n0);
-#pragma unroll
-                    for (int j = 0; j < T::LOAD_KB; j++)
-                        tma_load_2d(dst + T::PACKED_BYTES + j * T::X_STRIDE, &tmap_x, landed_bar(ps), k0 + j * 64, 0);
+                    // the four 64-element activation boxes of this K range in one request (chunked view of X)
+                    tma_load_3d(dst + T::PACKED_BYTES, &tmap_x, landed_bar(ps), 0, 0, k0 / 64);
                 }
             }
         }
@@ -203,9 +211,9 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 const int ps = pcount % LSTAGES;
                 const int jg = g % T::LOAD_GROUPS;             // group inside its load stage
                 const bool stage_ends = (jg == T::LOAD_GROUPS - 1 || g == w.kb_count - 1);
-                if (!__all_sync(0xffffffffu, mbar_wait(gempty_bar(slot), sphase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, slot))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(gempty_bar(slot), sphase ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_ACC, slot, 64))) { ok = false; break; }
                 // ready[slot] also tells that the load stage has landed: the dequantisers waited for it
-                if (!__all_sync(0xffffffffu, mbar_wait(ready_bar(slot), sphase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, slot))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(ready_bar(slot), sphase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, slot, 64))) { ok = false; break; }
                 tc_fence_after_sync();
                 if (elect_one_sync()) {
                     const uint32_t d_tmem = tmem_base + (uint32_t)(slot * MPAD);
@@ -228,6 +236,7 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       }
     } else if (warp >= 4 + 4 * T::FOLD) {
         // ------------------------------------------------------------------ dequantisers
+        if constexpr (T::DEQ_REGS < T::REGS_EVEN) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(T::DEQ_REGS));
         const int team = (warp - 4 - 4 * T::FOLD) >> 2;
         const int q = warp & 3;                       // TMEM lane quarter of this warp
         const int r = q * 32 + lane;                  // row of the tile this thread converts = TMEM lane
@@ -243,30 +252,36 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 const uint32_t pphase = ((uint32_t)(pcount / LSTAGES)) & 1u;
                 const int jg = g % T::LOAD_GROUPS;
                 if (jg == T::LOAD_GROUPS - 1 || g == w.kb_count - 1) pcount++;
-                if (gcount % T::TEAMS != team) continue;
-                if (!mbar_wait(landed_bar(ps), pphase, abort_flag, p.status, ST_TIMEOUT_DEQUANT, ps)) { ok = false; break; }
-                // packed row r: 128 bytes, 128B-swizzled by the TMA; group jg of the stage is its 16-byte chunks 4jg .. 4jg+3
-                const uint8_t *row = ld_ptr + ps * T::LOAD_STAGE_SMEM + r * 128;
-                uint32_t a[64];
+                // half h of group gcount is unit 2*gcount + h; team (2*gcount + h) % TEAMS converts it
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(row + (((4 * jg + c) ^ (r & 7)) << 4));
-                    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+                for (int h = 0; h < 2 && ok; h++) {
+                    if (((2 * gcount + h) % T::TEAMS) != team) continue;
+                    if (!mbar_wait(landed_bar(ps), pphase, abort_flag, p.status, ST_TIMEOUT_DEQUANT, ps, 64)) { ok = false; break; }
+                    // packed row r: 128 bytes, 128B-swizzled by the TMA; group jg of the stage is its 16-byte chunks 4jg .. 4jg+3,
+                    // this half the chunks 4jg + 2h and 4jg + 2h + 1 (64 K-elements)
+                    const uint8_t *row = ld_ptr + ps * T::LOAD_STAGE_SMEM + r * 128;
+                    uint32_t a[32];
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {                  // word i of chunk c = K-elements 32c + 8i .. +7 -> 4 column words
-                        uint32_t o[4];
-                        int4x8_to_bf16x8(words[i], o);
-                        a[16 * c + 4 * i] = o[0]; a[16 * c + 4 * i + 1] = o[1]; a[16 * c + 4 * i + 2] = o[2]; a[16 * c + 4 * i + 3] = o[3];
+                    for (int c = 0; c < 2; c++) {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(row + (((4 * jg + 2 * h + c) ^ (r & 7)) << 4));
+                        const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {              // word i of chunk c = K-elements 32c + 8i .. +7 -> 4 column words
+                            uint32_t o[4];
+                            int4x8_to_bf16x8(words[i], o);
+                            a[16 * c + 4 * i] = o[0]; a[16 * c + 4 * i + 1] = o[1]; a[16 * c + 4 * i + 2] = o[2]; a[16 * c + 4 * i + 3] = o[3];
+                        }
                     }
+                    // the slot's A columns are free once the MMAs of the group that used them last are done
+                    if (!mbar_wait(gdone_bar(slot), sphase ^ 1u, abort_flag, p.status, ST_TIMEOUT_DEQUANT, 16 + slot, 64)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    tmem_st_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(T::A_BASE + slot * T::A_COLS + 32 * h), a);
+                    tmem_st_wait();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(ready_bar(slot));
                 }
-                // the slot's A columns are free once the MMAs of the group that used them last are done
-                if (!mbar_wait(gdone_bar(slot), sphase ^ 1u, abort_flag, p.status, ST_TIMEOUT_DEQUANT, 16 + slot)) { ok = false; break; }
-                tc_fence_after_sync();
-                tmem_st_32x64(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(T::A_BASE + slot * T::A_COLS), a);
-                tmem_st_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(ready_bar(slot));
+                if (!ok) break;
             }
         }
     } else {
@@ -306,7 +321,7 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                     if (g0 + i >= w.kb_count) break;
                     const int b = gcount % SLOTS;
                     const float s = __uint_as_float((i & 1) ? (s_cur[i >> 1] & 0xffff0000u) : (s_cur[i >> 1] << 16));
-                    if (!mbar_wait(gdone_bar(b), (uint32_t)(gcount / SLOTS) & 1u, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, b)) { ok = false; break; }
+                    if (!mbar_wait(gdone_bar(b), (uint32_t)(gcount / SLOTS) & 1u, abort_flag, p.status, ST_TIMEOUT_EPILOGUE, b, 64)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * MPAD + fg * FC);
 #pragma unroll
@@ -377,7 +392,7 @@ struct W4A16TmemLauncher {
             attr_set[devid].store(true, std::memory_order_release);
         }
         CUtensorMap tx, tw;
-        rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, X, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, T::MPAD, CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = make_tmap_chunked(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, T::MPAD, T::LOAD_KB);
         if (rc != GEMM_OK) return rc;
         rc = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, Wq, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, 128, T::TILE_N, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != GEMM_OK) return rc;

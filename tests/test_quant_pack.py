@@ -133,7 +133,7 @@ def test_oracle_int4_quantiser_known_answers():
     assert list(packed[0, :2]) == [(7 & 0xf) | ((-7 & 0xf) << 4), 3 | ((-4 & 0xf) << 4)]
     s1 = float(o.bf16_bits_to_f32(sc)[1, 0])
     assert s1 == 0.0712890625
-    exp = [int(np.clip(np.rint(np.float32(v) / np.float32(s1)), -8, 7)) for v in (0.5, -0.25, 0.124, 0.0)]
+    exp = [int(np.clip(np.rint(np.float32(v) * (np.float32(1.0) / np.float32(s1))), -8, 7)) for v in (0.5, -0.25, 0.124, 0.0)]
     assert list(packed[1, :2]) == [(exp[0] & 0xf) | ((exp[1] & 0xf) << 4), (exp[2] & 0xf) | ((exp[3] & 0xf) << 4)]
     assert np.array_equal(o.int4_quantise(np.zeros((1, 128), np.float32))[1], o.f32_to_bf16_bits(np.ones((1, 1), np.float32)))
 
