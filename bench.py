@@ -350,11 +350,14 @@ def main():
         total_ms = float(t.item())
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region, plugin C ABI in the middle.
-    # One GPU: X and W up, Y down.  N GPUs: every rank brings X and its weight rows up and takes its 1/N of the
-    # rows of Y down, so the job delivers one full Y to the host.  Both overlap copy-in, kernels and copy-out by
-    # row chunks on three streams.
+    # One GPU: X and W up, Y down, overlapped by row chunks on three streams.  N GPUs: every rank brings 1/N of the
+    # rows of X and its weight rows up, the X slices are exchanged by one NCCL all-gather, and every rank takes its
+    # 1/N of the rows of Y down: the host sends X and W once and receives one full Y, whatever N is.
     slice_rows = M // world
-    Xh = torch.empty((M, K), dtype=torch.bfloat16).pin_memory(); Xh.copy_(X)
+    # the host holds X once: at N > 1 each rank has the pinned rows of its own slice (the fused path exchanges them over NVLink)
+    x_rows = slice_rows if (world > 1 and fused) else M
+    x_row0 = rank * slice_rows if (world > 1 and fused) else 0
+    Xh = torch.empty((x_rows, K), dtype=torch.bfloat16).pin_memory(); Xh.copy_(X[x_row0:x_row0 + x_rows])
     Wh = torch.empty((plan_rows, K), dtype=torch.bfloat16).pin_memory(); Wh.copy_(W)
     Yh = torch.empty((slice_rows, N), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(2, min(args.steps, 5))
@@ -428,7 +431,7 @@ def main():
             "roofline": roofline,
             "e2e": {"value": flops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                     "h2d_bytes_per_rank": h2d, "d2h_bytes_per_rank": d2h, "steps": e2e_steps,
-                    "note": "pinned host X and weight rows in, one full Y back to the host (each rank returns its 1/N of the rows), chunked over three streams"},
+                    "note": "pinned host X and W in (each rank its 1/N of the rows of X and its weight rows; X slices exchanged by one NCCL all-gather), one full Y back to the host (each rank its 1/N of the rows), copies overlapped with the kernels"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             # step time in SM clock cycles (ms x median SM MHz under load x 1000): compares runs that ran at different clocks

@@ -205,7 +205,8 @@ struct UmmaGemmTraits {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;   // bytes that arrive per stage
     static constexpr int OUT_CHUNK = 64;                   // output columns per TMA store (128 bytes of bf16)
     static constexpr int ACC_STRIDE = (BN_ + 31) / 32 * 32;  // TMEM columns between the two accumulator buffers
-    static constexpr int SF_COLS = SF_K_ATOMS * (1 + SF_N_ATOMS) * 4;   // TMEM columns of the staged scale factors
+    static constexpr int SF_COLS_ONE = SF_K_ATOMS * (1 + SF_N_ATOMS) * 4;   // TMEM columns of one k-block's scale factors
+    static constexpr int SF_COLS = 2 * SF_COLS_ONE;        // two sets: the next k-block's are copied in while this one's MMAs run
     // two FP32 accumulator buffers when they fit beside the scale factors, else one
     static constexpr int ACC_STAGE_COLS = MB_ * ACC_STRIDE;  // TMEM columns of one accumulator stage (MB_ row blocks side by side)
     static constexpr int ACC_STAGES = (2 * ACC_STAGE_COLS + SF_COLS <= 512) ? 2 : 1;
@@ -373,9 +374,24 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (cta_rank == 0) {   // every lane runs the loop; one elected lane issues (see elect_one_sync)
             const uint32_t instr = (T::OPK == OPK_BF16) ? make_idesc(UMMA_BF16, UMMA_BF16, T::UMMA_M, BN)
                                                          : make_idesc(UMMA_E4M3, UMMA_E4M3, T::UMMA_M, BN);
-            // scale factors live behind the accumulator buffers: X atoms, then W atoms
-            const uint32_t sfa_tmem = tmem_base + (uint32_t)(T::ACC_STAGES * T::ACC_STAGE_COLS);
-            const uint32_t sfb_tmem = sfa_tmem + (uint32_t)(T::SF_K_ATOMS * 4);
+            // Scale factors live behind the accumulator buffers, in two sets used in turn (X atoms, then W atoms).  The
+            // smem -> TMEM copies of k-block i+1 are issued right after the MMAs of k-block i, so they run while those
+            // MMAs execute instead of standing between two k-blocks' MMAs (tcgen05 operations of one thread execute in
+            // order; a set is rewritten only after the MMAs that read it were issued).
+            const uint32_t sf_tmem0 = tmem_base + (uint32_t)(T::ACC_STAGES * T::ACC_STAGE_COLS);
+            int sf_set = 0;            // set the current k-block's MMAs read
+            bool sf_ready = false;     // its copies were already issued (as the previous k-block's look-ahead)
+            auto copy_scale_atoms = [&](int st, int set) {
+                const uint32_t sfa = sf_tmem0 + (uint32_t)(set * T::SF_COLS_ONE), sfb = sfa + (uint32_t)(T::SF_K_ATOMS * 4);
+                const uint32_t sf_src = sf_base + st * T::SF_BYTES;
+#pragma unroll
+                for (int a = 0; a < T::SF_K_ATOMS; a++) {
+                    tmem_cp_sf_atom<CG>(sfa + a * 4, make_sf_atom_desc(sf_src + a * 512));
+#pragma unroll
+                    for (int j = 0; j < T::SF_N_ATOMS; j++)
+                        tmem_cp_sf_atom<CG>(sfb + (a * T::SF_N_ATOMS + j) * 4, make_sf_atom_desc(sf_src + T::SF_A_BYTES + (a * T::SF_N_ATOMS + j) * 512));
+                }
+            };
             int stage = 0;
             uint32_t phase = 0;
             int titer = 0;
@@ -397,16 +413,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     if (elect_one_sync()) {
                     const uint64_t a_desc = make_smem_desc_k128(a_base + stage * T::A_BYTES);
                     const uint64_t b_desc = make_smem_desc_k128(b_base + stage * T::B_BYTES);
+                    const uint32_t sfa_tmem = sf_tmem0 + (uint32_t)(sf_set * T::SF_COLS_ONE), sfb_tmem = sfa_tmem + (uint32_t)(T::SF_K_ATOMS * 4);
                     if constexpr (T::BLOCK_SCALED) {
-                        const uint32_t sf_src = sf_base + stage * T::SF_BYTES;
-#pragma unroll
-                        for (int a = 0; a < T::SF_K_ATOMS; a++) {
-                            tmem_cp_sf_atom<CG>(sfa_tmem + a * 4, make_sf_atom_desc(sf_src + a * 512));
-#pragma unroll
-                            for (int j = 0; j < T::SF_N_ATOMS; j++)
-                                tmem_cp_sf_atom<CG>(sfb_tmem + (a * T::SF_N_ATOMS + j) * 4,
-                                                make_sf_atom_desc(sf_src + T::SF_A_BYTES + (a * T::SF_N_ATOMS + j) * 512));
-                        }
+                        if (!sf_ready) copy_scale_atoms(stage, sf_set);
                     }
 #pragma unroll
                     for (int k = 0; k < T::UMMA_K_STEPS; k++) {
@@ -437,6 +446,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     }
                     __syncwarp();
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if constexpr (T::BLOCK_SCALED) {
+                        // look-ahead inside a tile: once the next k-block's bytes have landed, start its scale copies now
+                        sf_ready = false;
+                        if (kb + 1 < w.kb_count) {
+                            if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage))) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            sf_set ^= 1;
+                            if (elect_one_sync()) copy_scale_atoms(stage, sf_set);
+                            __syncwarp();
+                            sf_ready = true;
+                        }
+                    }
                 }
                 if (!ok) break;
                 if (elect_one_sync()) {

@@ -104,7 +104,7 @@ struct GemmConfig {
         const size_t barriers = (2 * (size_t)num_stages + 4) * 8 + 16;
         const size_t ring = num_stages * (a + b) + sf_ring + barriers + 1024;
         // a single accumulator stage (two do not fit in TMEM) gets four staging buffers when they fit
-        const bool one_acc_stage = 2 * mb * (((size_t)bn + 31) / 32 * 32) + k_atoms * (1 + n_atoms) * 4 > 512;
+        const bool one_acc_stage = 2 * mb * (((size_t)bn + 31) / 32 * 32) + 2 * k_atoms * (1 + n_atoms) * 4 > 512;
         const size_t bufs = (one_acc_stage && ring + 4 * 128 * 64 * 2 <= 232448) ? 4 : 2;
         const size_t staging = (split_k <= 1 && epi == 1) ? bufs * 128 * 64 * 2 : 0;
         return ring + staging;
@@ -337,7 +337,8 @@ inline double heuristic_ms(const GemmConfig &c, int M, int N, int K, int sms = 1
     if (c.split_k == 0) {         // stream-K: every slot gets the same share
         const double share = tiles / (tiles < slots ? tiles : slots);
         const double tt = share * unit_flops / slot_flops, tm = share * unit_bytes / slot_bw;
-        t = (tt > tm ? tt : tm) * (tiles < slots ? tiles / slots : 1.0) + 4e-6;
+        // + the FP32 partial tiles (two per CTA) written, read back and reduced by the fix-up kernel
+        t = (tt > tm ? tt : tm) * (tiles < slots ? tiles / slots : 1.0) + 4.0 * slots * c.bm * c.bn * 4.0 / 5.0e12 + 4e-6;
     } else {
         const double rounds = std::ceil(tiles * split / slots);
         const double tt = unit_flops / slot_flops, tm = unit_bytes / slot_bw;

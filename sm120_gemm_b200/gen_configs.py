@@ -90,7 +90,7 @@ class GemmConfig:
         sf_ring = -(-self.num_stages * sf // 1024) * 1024
         ring = self.num_stages * (a + b) + sf_ring + barriers + 1024
         # one accumulator stage (two do not fit in the 512 TMEM columns beside the scale factors): four staging buffers if they fit
-        acc_stages = 2 if 2 * self.mb * (-(-self.bn // 32) * 32) + k_atoms * (1 + n_atoms) * 4 <= 512 else 1
+        acc_stages = 2 if 2 * self.mb * (-(-self.bn // 32) * 32) + 2 * k_atoms * (1 + n_atoms) * 4 <= 512 else 1
         bufs = 4 if acc_stages == 1 and ring + 4 * 128 * 64 * 2 <= MAX_SMEM else 2
         staging = bufs * 128 * 64 * 2 if epi == 1 else 0
         return ring + staging
@@ -141,7 +141,7 @@ def heuristic_ms(c: GemmConfig, M: int, N: int, K: int, sms: int = 148) -> float
     if c.split_k == 0:
         share = tiles / (tiles if tiles < slots else slots)
         tt, tm = share * unit_flops / slot_flops, share * unit_bytes / slot_bw
-        t = (tt if tt > tm else tm) * (tiles / slots if tiles < slots else 1.0) + 4e-6
+        t = (tt if tt > tm else tm) * (tiles / slots if tiles < slots else 1.0) + 4.0 * slots * c.bm * c.bn * 4.0 / 5.0e12 + 4e-6
     else:
         rounds = float(math.ceil(tiles * split / slots))
         tt, tm = unit_flops / slot_flops, unit_bytes / slot_bw

@@ -61,18 +61,21 @@ class HostGemm:
 
 
 class ShardedHostGemm:
-    """The same host-buffer call on the N-sharded path (one process per GPU): every rank brings the full X and
-    its own weight rows from pinned host memory, the row chunks run through the fused GEMM + all-gather
-    (``FusedNShardedGemm``: every rank's device Y receives every column block), and each rank returns only its
-    1/world slice of the ROWS of Y to the host, so the ranks together deliver one full Y (M*N*2 bytes in total,
-    not world times that).  Copy in, kernels and copy out overlap on three streams, chunk by chunk; a chunk is
-    copied out after the cross-rank barrier that follows its GEMM."""
+    """The same host-buffer call on the N-sharded path (one process per GPU).  Nothing is sent from the host twice:
+    every rank brings its own 1/world of the ROWS of X and its own weight rows from pinned host memory, the X
+    slices are exchanged between the GPUs by one NCCL all-gather over NVLink (each rank needs all of X), the row
+    chunks then run through the fused GEMM + all-gather of the result (``FusedNShardedGemm``: every rank's device Y
+    receives every column block), and each rank returns only its 1/world slice of the rows of Y to the host.  Host
+    traffic of the whole job per call: M*K*2 + N*K*2 bytes up, M*N*2 bytes down, whatever the number of GPUs.
+    The copy out of a chunk overlaps the kernels of the next ones; a chunk is copied out after the cross-rank
+    barrier that follows its GEMM."""
 
-    def __init__(self, fused, chunk_rows: int = 2048, device_X=None, device_W=None):
+    def __init__(self, fused, chunk_rows: int = 2048, device_X=None, device_W=None, group=None):
         import torch
 
         self.torch = torch
         self.f = fused
+        self.group = group
         M, world = fused.M, fused.plan.world
         if M % world != 0:
             raise ValueError(f"M={M} rows do not split over {world} ranks")
@@ -85,12 +88,14 @@ class ShardedHostGemm:
         self.X = device_X if device_X is not None else torch.empty((M, fused.K), dtype=torch.bfloat16, device=dev)
         self.W = device_W if device_W is not None else torch.empty((fused.plan.rows, fused.K), dtype=torch.bfloat16, device=dev)
         self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
-        self.h2d_bytes = (M + fused.plan.rows) * fused.K * 2
+        self.h2d_bytes = (self.slice_rows + fused.plan.rows) * fused.K * 2
         self.d2h_bytes = self.slice_rows * fused.N * 2
 
-    def run(self, Xh, Wh_shard, Yh_slice) -> int:
-        """Xh: pinned M x K; Wh_shard: pinned (N/world) x K; Yh_slice: pinned (M/world) x N, receives rows
-        [rank*M/world, (rank+1)*M/world) of Y.  Returns the number of GEMM launches."""
+    def run(self, Xh_slice, Wh_shard, Yh_slice) -> int:
+        """Xh_slice: pinned (M/world) x K, rows [rank*M/world, (rank+1)*M/world) of X; Wh_shard: pinned (N/world) x K;
+        Yh_slice: pinned (M/world) x N, receives the same rows of Y.  Returns the number of GEMM launches."""
+        import torch.distributed as dist
+
         from . import dispatch_ex
 
         t, f = self.torch, self.f
@@ -102,16 +107,20 @@ class ShardedHostGemm:
         Y, handle = f.buffers[buf], f.handles[buf]
         if not f.double_buffer:
             handle.barrier()
+        mine = self.X[self.row0:self.row0 + self.slice_rows]
         with t.cuda.stream(self.s_in):
+            mine.copy_(Xh_slice, non_blocking=True)
+            x_landed = t.cuda.Event()
+            x_landed.record(self.s_in)
             self.W.copy_(Wh_shard, non_blocking=True)
+            w_landed = t.cuda.Event()
+            w_landed.record(self.s_in)
+        cur.wait_event(x_landed)
+        dist.all_gather_into_tensor(self.X, mine, group=self.group)     # in place: each rank's slice is already where it belongs
+        cur.wait_event(w_landed)
         launches = 0
         for r0 in range(0, f.M, self.chunk):
             r1 = r0 + self.chunk
-            with t.cuda.stream(self.s_in):
-                self.X[r0:r1].copy_(Xh[r0:r1], non_blocking=True)
-                landed = t.cuda.Event()
-                landed.record(self.s_in)
-            cur.wait_event(landed)
             dispatch_ex(f.kernel, f._args(buf, r0, r1 - r0, self.X[r0:r1].data_ptr(), self.W.data_ptr(), cur.cuda_stream))
             launches += 1
             handle.barrier()                      # every rank's blocks of these rows have landed here

@@ -68,9 +68,10 @@ def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel):
         ok += [bool(torch.equal(y1, Yref)), bool(torch.equal(y1b, Yref)), bool(torch.equal(y2, Yref2))]
         used_multicast = bool(fused.multicast)
         if double_buffer:
-            # host buffers in, this rank's slice of the rows of Y out, chunked over three streams
+            # host buffers in (this rank's rows of X, exchanged over NVLink; its weight rows), its rows of Y out
             shg = ShardedHostGemm(fused, chunk_rows=M // world // 2)
-            Xh, Wh = X.cpu().pin_memory(), Wr.cpu().pin_memory()
+            r0 = rank * (M // world)
+            Xh, Wh = X[r0:r0 + M // world].cpu().pin_memory(), Wr.cpu().pin_memory()      # this rank's rows of X only
             Yh = torch.empty((M // world, N), dtype=torch.bfloat16).pin_memory()
             shg.run(Xh, Wh, Yh)
             torch.cuda.synchronize()
