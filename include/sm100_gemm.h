@@ -92,7 +92,8 @@ typedef struct GemmArgs {
     /* Optional.  Multicast (NVSwitch) address of that same symmetric matrix: a store to it lands in every     */
     /* rank's copy.  When non-NULL the epilogue issues one multimem store per 16 bytes instead of one TMA      */
     /* store per peer, so each result byte leaves this GPU once; y_num_peers must still be > 0 and N a         */
-    /* multiple of 8.  Every process bound to the multicast object must stay alive until the stores are done.  */
+    /* multiple of 8, and y_peers[0] must be THIS GPU's own matrix (the 512-row-tile kernels store a tile there */
+    /* first and forward it).  Every process bound to the multicast object must stay alive until the stores are done. */
     void *y_multicast;
     /* Fused output transform, honoured by the fused-epilogue plugins only (`_e2` in the name; every other plugin  */
     /* answers GEMM_ERR_ARG when one of these is set):  D = act(alpha * (X * W^T) + beta * C + bias), written as   */

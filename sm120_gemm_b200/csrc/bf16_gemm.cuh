@@ -112,6 +112,7 @@ struct GemmParams {
     float *amax;          // nullptr = not wanted
     int act;              // ACT_*
     int y_dtype;          // YOUT_*
+    int tail_full;        // two-row-block kernels: whole tiles before the halved last wave (see WorkSched); < 0: no halving
     int test_withhold_kb; // wait-expiry test build only: the producer stops before this k-block (< 0: never)
 };
 
@@ -121,6 +122,7 @@ struct WorkItem {
     int kb_begin;   // first k-block (units of BK elements)
     int kb_count;
     int part;       // -1: the whole K range -> bf16 output; >= 0: FP32 partial (split index, or stream-K slot 0/1)
+    int half;       // two-row-block kernels, last wave: -1 the whole tile, 0 / 1 only its upper / lower 256 rows (see WorkSched)
 };
 
 // Work distribution.  SPLIT_K >= 1: tiles x SPLIT_K equal K slices, dealt round-robin over the
@@ -129,13 +131,20 @@ struct WorkItem {
 // long range per CTA, so every SM streams the same number of bytes whatever the tile count; a
 // range that does not cover a tile's whole K leaves an FP32 partial in the CTA's slot 0 (its
 // first item) or slot 1 (its last item), which streamk_reduce_kernel adds up in K order.
+//
+// Halved last wave (SPLIT_K == 1, two-row-block kernels only; p.tail_full >= 0): when the tiles left for the last
+// round of the grid are at most half as many as the clusters, every one of them is dealt as two halves of 256 rows,
+// each computed like a 256 x 256 tile by a cluster of its own, so the last round takes half as long.  Virtual
+// indices below tail_full are whole tiles; index tail_full + 2i + h is half h of tile tail_full + i.
 template <int SPLIT_K>
 struct WorkSched {
     long long u, u_begin, u_end;   // stream-K: unit range;  fixed: virtual tile index, stride, total
     int kb_per_tile;
+    int tail_full;
     __device__ WorkSched(int cluster_id, int num_clusters, const GemmParams &p)
     {
         kb_per_tile = p.num_k_blocks;
+        tail_full = -1;
         if constexpr (SPLIT_K == 0) {
             const long long units = (long long)p.num_m_blocks * p.num_n_blocks * kb_per_tile;
             u_begin = units * cluster_id / num_clusters;
@@ -145,11 +154,16 @@ struct WorkSched {
             u = cluster_id;
             u_begin = num_clusters;
             u_end = (long long)p.num_m_blocks * p.num_n_blocks * SPLIT_K;
+            if constexpr (SPLIT_K == 1) {
+                tail_full = p.tail_full;
+                if (tail_full >= 0) u_end = tail_full + 2 * (u_end - tail_full);
+            }
         }
     }
     __device__ bool next(WorkItem &w)
     {
         if (u >= u_end) return false;
+        w.half = -1;
         if constexpr (SPLIT_K == 0) {
             w.tile = (int)(u / kb_per_tile);
             w.kb_begin = (int)(u - (long long)w.tile * kb_per_tile);
@@ -164,6 +178,13 @@ struct WorkSched {
             w.kb_begin = split * kb_per_tile;
             w.kb_count = kb_per_tile;
             w.part = SPLIT_K > 1 ? split : -1;
+            if constexpr (SPLIT_K == 1) {
+                if (tail_full >= 0 && u >= tail_full) {
+                    const int unit = (int)(u - tail_full);
+                    w.tile = tail_full + (unit >> 1);
+                    w.half = unit & 1;
+                }
+            }
             u += u_begin;
         }
         return true;
@@ -226,7 +247,12 @@ struct UmmaGemmTraits {
     // Kernels with a single accumulator buffer cannot hide the epilogue behind the next main loop, so they
     // drain it with two epilogue groups of four warps (alternate 64- or 16-column pieces) instead of one.
     static constexpr int EPI_GROUPS = ACC_STAGES == 1 ? 2 : 1;
-    static constexpr int THREADS = 128 + 128 * EPI_GROUPS;
+    // Two row blocks per CTA have a single accumulator stage, so their epilogue is on the critical path of the next
+    // tile; in an N-sharded run its multicast stores would be paced by NVLink (a few GB/s per SM).  Such kernels
+    // therefore store the tile to the LOCAL result with TMA stores and four more warps ("senders") forward finished
+    // tiles from there to the multicast address while the next tile's MMAs run.
+    static constexpr int SENDER_WARPS = (MB_ == 2) ? 4 : 0;
+    static constexpr int THREADS = 128 + 128 * EPI_GROUPS + 32 * SENDER_WARPS;
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "BN (the UMMA N extent) is a multiple of 16 up to 256");
     static_assert(EPI != EPI_TMA || BN_ % 64 == 0, "the TMA-store epilogue writes 64-column boxes");
     static_assert((BN_ / CG_) % 8 == 0, "each CTA loads whole 8-row swizzle groups of W");
@@ -266,6 +292,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (bar_base - smem_base) + 8u * T::NUM_BARRIERS);
     volatile uint32_t *abort_flag = tmem_slot + 1;
+    // epilogue -> senders: one counter per epilogue group (two words), the tiles whose row block that group has stored
+    // completely, counted up for ever (a counter, not an mbarrier: the senders may fall more than one tile behind,
+    // which a phase bit cannot express)
+    volatile uint32_t *stored_count = tmem_slot + 2;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -282,6 +312,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             mbar_init(tfull_bar(a), 1);
             mbar_init(tempty_bar(a), CG * 4 * T::EPI_GROUPS);   // one arrival per epilogue warp of every CTA of the group
         }
+        stored_count[0] = 0;
+        stored_count[1] = 0;
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
@@ -335,8 +367,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             while (ok && sched.next(w)) {
                 int mb, nb;
                 tile_to_mn(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
-                const int row_x = mb * T::BM + (int)cta_rank * T::BM_CTA;
+                // half of a tile (last wave of a two-row-block kernel): 256 consecutive rows, 128 per CTA, into row block 0
+                const bool half = T::MB == 2 && w.half >= 0;
+                const int row_x = half ? mb * T::BM + w.half * (T::BM / 2) + (int)cta_rank * 128 : mb * T::BM + (int)cta_rank * T::BM_CTA;
                 const int row_w = nb * BN + (int)cta_rank * T::BN_CTA;
+                const uint32_t stage_bytes = half ? T::STAGE_BYTES - T::A_BYTES / 2 : T::STAGE_BYTES;
                 SM100_BOUNDS(row_x >= 0 && row_x < p.M + T::BM && row_w >= 0 && row_w < p.N + BN, ST_BOUNDS_LOAD_ROW, w.tile);
                 for (int kb = 0; kb < w.kb_count; kb++) {
                     const int kx = (w.kb_begin + kb) * T::BK_COORD;
@@ -359,10 +394,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         tma_load_2d(a_base + stage * T::A_BYTES, &tmap_x, full_bar(stage), kx, row_x);
                         if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, w.kb_begin + kb, row_x, nb * BN, full_bar(stage));
                     } else {
-                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * T::STAGE_BYTES);
+                        if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * stage_bytes);
                         const uint32_t fb = full_leader + 8u * stage;
                         tma_load_2d_pair(b_base + stage * T::B_BYTES, &tmap_w, fb, kx, row_w);
-                        tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x);
+                        // the scale-factor map of X is free in these kernels: it carries X again, with a box of 128 rows
+                        if (half) tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_sfx, fb, kx, row_x);
+                        else tma_load_2d_pair(a_base + stage * T::A_BYTES, &tmap_x, fb, kx, row_x);
                         if constexpr (T::BLOCK_SCALED) load_scale_atoms(stage, w.kb_begin + kb, row_x, nb * BN, fb);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -433,11 +470,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         if constexpr (T::OPK == OPK_BF16) {
 #pragma unroll
                             for (int blk = 0; blk < T::MB; blk++)   // row block blk: X rows 128*blk.. of this CTA, 16 KB further on
+                                if (blk == 0 || w.half < 0)
                                 umma_f16<CG>(d_tmem + (uint32_t)(blk * T::ACC_STRIDE), advance_desc_k(a_desc + (uint64_t)(blk * 1024), k),
                                              advance_desc_k(b_desc, k), instr, accumulate);
                         } else {
 #pragma unroll
                             for (int blk = 0; blk < T::MB; blk++)
+                                if (blk == 0 || w.half < 0)
                                 umma_f8f6f4<CG>(d_tmem + (uint32_t)(blk * T::ACC_STRIDE), advance_desc_k(a_desc + (uint64_t)(blk * 1024), k),
                                                 advance_desc_k(b_desc, k), instr, accumulate);
                         }
@@ -469,7 +508,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 __syncwarp();
             }
         }
-    } else if (warp >= 4) {
+    } else if (warp >= 4 && warp < 4 + 4 * T::EPI_GROUPS) {
         // ------------------------------------------------------------------ epilogue
         constexpr int EG = T::EPI_GROUPS;
         const int eg = (warp - 4) >> 2;            // epilogue group of this warp
@@ -487,7 +526,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             tile_to_mn(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
             // two row blocks per CTA: epilogue group eg drains the accumulator of row block eg
             const int blk = (T::MB == 2) ? eg : 0;
-            const int m0 = mb * T::BM + (int)cta_rank * T::BM_CTA + blk * 128;
+            const bool half = T::MB == 2 && w.half >= 0;     // only row block 0 holds a result: group 1 just hands the buffer back
+            const int m0 = half ? mb * T::BM + w.half * (T::BM / 2) + (int)cta_rank * 128 : mb * T::BM + (int)cta_rank * T::BM_CTA + blk * 128;
             const int n0 = nb * BN;
             const int acc = titer % T::ACC_STAGES;
             const uint32_t acc_phase = (titer / T::ACC_STAGES) & 1;
@@ -508,7 +548,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 }
             };
 
-            if (T::SPLIT_K == 0 && w.part >= 0) {
+            if (half && eg == 1) {
+                release_acc();
+                if constexpr (T::SENDER_WARPS > 0) {
+                    if (p.y_mc != nullptr && epi_tid == 0) smem_counter_add_release(smem_u32(const_cast<uint32_t *>(stored_count + eg)));
+                }
+            } else if (T::SPLIT_K == 0 && w.part >= 0) {
                 // stream-K partial: the CTA's private slot, tile-local [BM][BN] layout, no bounds
                 float *slot = p.workspace + ((size_t)(2 * cluster_id + w.part) * T::BM + cta_rank * T::BM_CTA + row_in_tile) * BN;
 #pragma unroll 1
@@ -571,7 +616,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     if (j + J_STEP >= BN / 64) release_acc();       // this group's last piece of the accumulator
                     fence_proxy_async_smem();
                     named_bar_sync(bar_a, 128);
-                    if (p.y_mc != nullptr) {
+                    if (T::SENDER_WARPS == 0 && p.y_mc != nullptr) {
                         // all-gather through NVSwitch: eight lanes read one staged 128-byte row piece and store it
                         // once to the multicast address (16 rows per pass); the barrier at the top of the next
                         // round keeps writers off this buffer until every reader is done
@@ -592,6 +637,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         tma_store_commit();
                     }
                     buf ^= 1;
+                }
+                if constexpr (T::SENDER_WARPS > 0) {
+                    // N-sharded run: this group's row block of the tile is on its way to the local result; once the
+                    // stores are complete the senders may read it back (from L2) and forward it to the other ranks
+                    if (p.y_mc != nullptr && epi_tid == 0) {
+                        tma_store_wait<0>();
+                        fence_proxy_async_global();
+                        smem_counter_add_release(smem_u32(const_cast<uint32_t *>(stored_count + eg)));
+                    }
                 }
             } else if constexpr (T::EPI == EPI_FUSED) {
                 // D = act(alpha * acc + beta * C + bias) from registers; bf16 out (32 bytes per thread and step) or
@@ -696,6 +750,48 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
         if constexpr (T::EPI == EPI_TMA) {
             if (epi_tid == 0) tma_store_wait<0>();
+        }
+    } else if (warp >= 4 + 4 * T::EPI_GROUPS) {
+        // ------------------------------------------------------------------ senders (two-row-block kernels, N-sharded run)
+        if constexpr (T::SENDER_WARPS > 0) {
+            if (p.y_mc != nullptr) {
+                const int st = threadIdx.x - (128 + 128 * T::EPI_GROUPS);    // 0 .. 127
+                const int chunk = st & 31;                                    // 16-byte piece of a 512-byte tile row
+                const bf16 *local = static_cast<const bf16 *>(p.Y);          // this rank's own copy of the result
+                int titer = 0;
+                WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
+                WorkItem w;
+                for (; sched.next(w); titer++) {
+                    int mb, nb;
+                    tile_to_mn(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_n, mb, nb);
+                    const bool half = w.half >= 0;
+                    const int m0 = half ? mb * T::BM + w.half * (T::BM / 2) + (int)cta_rank * 128 : mb * T::BM + (int)cta_rank * T::BM_CTA;
+                    const int rows = half ? 128 : T::BM_CTA;
+                    const int col = nb * BN + chunk * 8;
+                    // work item number titer is stored once both groups have counted it
+                    if (!smem_counter_wait(smem_u32(const_cast<uint32_t *>(stored_count)), (uint32_t)(titer + 1), abort_flag, p.status, ST_TIMEOUT_EPILOGUE, 8) ||
+                        !smem_counter_wait(smem_u32(const_cast<uint32_t *>(stored_count + 1)), (uint32_t)(titer + 1), abort_flag, p.status, ST_TIMEOUT_EPILOGUE, 9))
+                        break;
+                    if (col + 8 > p.N) continue;
+                    const size_t off0 = (size_t)p.y_col_offset + col;
+                    // one warp per row and pass, four rows in flight per thread: loads come from L2 (the tile was just stored),
+                    // bypassing L1, which may hold this address from an earlier step
+#pragma unroll 1
+                    for (int r0 = st >> 5; r0 < rows; r0 += 16) {
+                        uint4 v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int r = m0 + r0 + 4 * u;
+                            if (r < p.M) v[u] = __ldcg(reinterpret_cast<const uint4 *>(local + (size_t)r * p.y_ld + off0));
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int r = m0 + r0 + 4 * u;
+                            if (r < p.M) multimem_st_v4(p.y_mc + (size_t)r * p.y_ld + off0, v[u].x, v[u].y, v[u].z, v[u].w);
+                        }
+                    }
+                }
+            }
         }
     }
 
@@ -969,6 +1065,11 @@ struct UmmaGemmLauncher {
         rc = make_tmap_2d(&tw, dt, W, row_elems, (uint64_t)N, row_bytes, T::BK_COORD, T::BN_CTA, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != GEMM_OK) return rc;
         CUtensorMap tsfx = tx, tsfw = tx;   // placeholders unless block-scaled
+        if (T::MB == 2) {
+            // X again with a box of 128 rows, for the halves of the last wave
+            rc = make_tmap_2d(&tsfx, dt, X, row_elems, (uint64_t)M, row_bytes, T::BK_COORD, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc != GEMM_OK) return rc;
+        }
         if (T::BLOCK_SCALED) {
             const uint64_t k_atoms = ((uint64_t)K + 127) / 128;
             rc = make_tmap_2d(&tsfx, CU_TENSOR_MAP_DATA_TYPE_UINT8, sf_x, 256, ((uint64_t)M + 127) / 128 * k_atoms * 2, 256, 256, 2,
@@ -984,6 +1085,15 @@ struct UmmaGemmLauncher {
                 return set_error(GEMM_ERR_ARG, "multicast stores need N %% 8 == 0 and a 16-byte aligned address");
             y_targets = 0;
             tys.m[0] = tx;
+            if (T::SENDER_WARPS > 0) {
+                // the tile goes to this rank's own matrix first (peers[0], by contract the local one when a multicast
+                // address is given); the sender warps forward it from there
+                if (!yt->peers[0]) return set_error(GEMM_ERR_ARG, "null local destination (y_peers[0])");
+                y_targets = 1;
+                rc = make_tmap_2d(&tys.m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, yt->peers[0], (uint64_t)(yt->col_offset + N), (uint64_t)M,
+                                  (uint64_t)yt->ld * 2, T::OUT_CHUNK, T::EPI_ROWS, CU_TENSOR_MAP_SWIZZLE_128B);
+                if (rc != GEMM_OK) return rc;
+            }
         } else if (fused_gather) {
             // one map per rank's matrix; the extent stops at this block's last column so that a partial last
             // tile is clipped there and cannot spill into the next rank's columns
@@ -1010,7 +1120,7 @@ struct UmmaGemmLauncher {
         p.group_n = band_width(T::BN, T::MB);
         // with a single accumulator stage the epilogue's wake-up is on the critical path of every tile
         p.wait_sleep_ns = wait_sleep_ns(T::ACC_STAGES == 1 ? (p.num_k_blocks < 16 ? p.num_k_blocks : 16) : p.num_k_blocks);
-        p.Y = Y;
+        p.Y = (fused_gather && yt->multicast && T::SENDER_WARPS > 0) ? yt->peers[0] : Y;
         p.workspace = workspace;
         p.alpha = alpha;
         p.status = dev->status;
@@ -1032,6 +1142,20 @@ struct UmmaGemmLauncher {
         // compute-bound shapes only: a memory-bound one (M <= 128 rows) wants every SM's loads in flight
         rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &grid, M >= 512);
         if (rc != GEMM_OK) return rc;
+        p.tail_full = -1;
+        if (T::MB == 2 && T::SPLIT_K == 1) {
+            // the tiles of the last round, when they would leave at least half of the clusters idle, go out as halves
+            int full_grid = 0;
+            rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &full_grid, false);
+            if (rc != GEMM_OK) return rc;
+            const int clusters = full_grid / T::CG;
+            const int tiles = p.num_m_blocks * p.num_n_blocks;
+            const int rest = tiles % clusters;
+            if (tiles > clusters && rest > 0 && 2 * rest <= clusters) {
+                p.tail_full = tiles - rest;
+                grid = full_grid;
+            }
+        }
         if (T::SPLIT_K == 0 && grid > STREAMK_MAX_CTAS) grid = STREAMK_MAX_CTAS - STREAMK_MAX_CTAS % T::CG;
 
         cudaLaunchConfig_t cfg = {};

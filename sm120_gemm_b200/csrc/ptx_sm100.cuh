@@ -109,6 +109,12 @@ __device__ __forceinline__ void fence_proxy_async_smem()
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// orders this thread's completed bulk (async-proxy) stores to global memory before what it does next in the generic proxy
+__device__ __forceinline__ void fence_proxy_async_global()
+{
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -160,6 +166,39 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (ns < sleep_cap_ns) ns <<= 1;
         }
         if ((++spins & (sleep_cap_ns ? 0xfu : 0xffu)) == 0) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                if (status != nullptr && atomicCAS(status, 0u, code) == 0u) {
+                    status[1] = blockIdx.x;
+                    status[2] = detail;
+                }
+                return false;
+            }
+        }
+    }
+}
+
+// A counter in shared memory as a one-way signal inside a CTA: the producer adds with release semantics, the consumer
+// polls with acquire semantics until the count reaches its target.  Bounded like mbar_wait.
+__device__ __forceinline__ void smem_counter_add_release(uint32_t addr)
+{
+    asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(addr) : "memory");
+}
+
+__device__ __forceinline__ bool smem_counter_wait(uint32_t addr, uint32_t target, volatile uint32_t *abort_flag, uint32_t *status, uint32_t code,
+                                                  uint32_t detail)
+{
+    long long t0 = 0;
+    uint32_t spins = 0;
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+        if ((int32_t)(v - target) >= 0) return true;
+        __nanosleep(256);
+        if ((++spins & 0xfu) == 0) {
             if (*abort_flag) return false;
             const long long now = clock64();
             if (t0 == 0) t0 = now;

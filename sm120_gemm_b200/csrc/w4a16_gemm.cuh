@@ -78,20 +78,21 @@ struct W4A16Traits {
 };
 
 // 8 signed int4 (two's complement nibbles, nibble j = element j) -> four bf16x2 holding the exact
-// integers.  Flipping each nibble's top bit turns it into q+8 in 0..15; OR-ing that into the
-// mantissa of 128.0 (0x4300) gives the bf16 number 128+(q+8) exactly, and subtracting 136 leaves q.
+// integers.  Flipping a nibble's top bit turns it into q+8 in 0..15; placed in the mantissa of 128.0
+// (0x4300) that is the bf16 number 128+(q+8) exactly, and subtracting 136 leaves q.  One lop3 does the
+// mask, the flip and the merge: with m = 0x000f000f and c = 0x43084308 it computes m ? (y ^ c) : c
+// per bit (truth table 0x6A), where c carries both the exponent and the bit to flip.
 __device__ __forceinline__ void int4x8_to_bf16x8(uint32_t w, uint32_t (&out)[4])
 {
-    const uint32_t x = w ^ 0x88888888u;
-    const uint32_t x4 = x >> 4;
+    const uint32_t w4 = w >> 4;
     const uint32_t bias = 0x43084308u;   // bf16x2 {136, 136}
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        // byte j of x -> bits [0,8), byte j of x4 -> bits [16,24): low halves hold nibbles 2j and 2j+1
-        uint32_t sel = 0x4040u | (uint32_t)j | ((uint32_t)(4 + j) << 8);   // bytes: [j of x, 0-filler, j of x4, filler]
+        // byte j of w -> bits [0,8), byte j of w4 -> bits [16,24): low halves hold nibbles 2j and 2j+1
+        uint32_t sel = 0x4040u | (uint32_t)j | ((uint32_t)(4 + j) << 8);   // bytes: [j of w, filler, j of w4, filler]
         uint32_t y;
-        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(y) : "r"(x), "r"(x4), "r"(sel));
-        y = (y & 0x000f000fu) | 0x43004300u;
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(y) : "r"(w), "r"(w4), "r"(sel));
+        asm("lop3.b32 %0, %1, 0x000f000f, 0x43084308, 0x6A;" : "=r"(y) : "r"(y));
         asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(out[j]) : "r"(y), "r"(bias));
     }
 }

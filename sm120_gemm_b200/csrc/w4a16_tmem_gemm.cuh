@@ -205,6 +205,8 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         WorkItem w;
         bool ok = true;
         while (ok && sched.next(w)) {
+            // (Issuing two groups at a time with their MMAs alternating, so that the two accumulation chains overlap, was
+            // measured 4-10 % slower: the issuer then waits for the second group's weights before it starts the first.)
             for (int g = 0; g < w.kb_count; g++, gcount++) {
                 const int slot = gcount % SLOTS;
                 const uint32_t sphase = ((uint32_t)(gcount / SLOTS)) & 1u;
@@ -240,49 +242,54 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const int team = (warp - 4 - 4 * T::FOLD) >> 2;
         const int q = warp & 3;                       // TMEM lane quarter of this warp
         const int r = q * 32 + lane;                  // row of the tile this thread converts = TMEM lane
-        int gcount = 0, pcount = 0;
+        // Units of work are half groups, numbered 2 * (group counter) + half over the whole run of this CTA; team t converts
+        // the units that are t modulo TEAMS.  The loop visits only those: all index arithmetic happens once per converted
+        // unit (a warp that stepped through every group and skipped the others' spent as many instructions on the
+        // stepping as on the conversion).
+        int gcount0 = 0, pcount0 = 0;                  // groups and load stages before the current work item
         WorkSched<0> sched(cta, num_ctas, sp);
         WorkItem w;
         bool ok = true;
         while (ok && sched.next(w)) {
-            for (int g = 0; g < w.kb_count; g++, gcount++) {
-                const int slot = gcount % SLOTS;
-                const uint32_t sphase = ((uint32_t)(gcount / SLOTS)) & 1u;
-                const int ps = pcount % LSTAGES;
-                const uint32_t pphase = ((uint32_t)(pcount / LSTAGES)) & 1u;
-                const int jg = g % T::LOAD_GROUPS;
-                if (jg == T::LOAD_GROUPS - 1 || g == w.kb_count - 1) pcount++;
-                // half h of group gcount is unit 2*gcount + h; team (2*gcount + h) % TEAMS converts it
+            const int u0 = 2 * gcount0, u_end = u0 + 2 * w.kb_count;
+            int u = u0 + (team + T::TEAMS - u0 % T::TEAMS) % T::TEAMS;
+#pragma unroll 1
+            for (; u < u_end; u += T::TEAMS) {
+                const int gl = (u - u0) >> 1, h = u & 1;           // group inside the work item, half of the group
+                const int gc = u >> 1;                             // group counter of the run
+                const int slot = gc % SLOTS;
+                const uint32_t sphase = ((uint32_t)(gc / SLOTS)) & 1u;
+                const int pc = pcount0 + gl / T::LOAD_GROUPS;      // load stage counter: LOAD_GROUPS groups per stage
+                const int ps = pc % LSTAGES;
+                const uint32_t pphase = ((uint32_t)(pc / LSTAGES)) & 1u;
+                const int jg = gl % T::LOAD_GROUPS;
+                if (!mbar_wait(landed_bar(ps), pphase, abort_flag, p.status, ST_TIMEOUT_DEQUANT, ps, 64)) { ok = false; break; }
+                // packed row r: 128 bytes, 128B-swizzled by the TMA; group jg of the stage is its 16-byte chunks 4jg .. 4jg+3,
+                // this half the chunks 4jg + 2h and 4jg + 2h + 1 (64 K-elements)
+                const uint8_t *row = ld_ptr + ps * T::LOAD_STAGE_SMEM + r * 128;
+                uint32_t a[32];
 #pragma unroll
-                for (int h = 0; h < 2 && ok; h++) {
-                    if (((2 * gcount + h) % T::TEAMS) != team) continue;
-                    if (!mbar_wait(landed_bar(ps), pphase, abort_flag, p.status, ST_TIMEOUT_DEQUANT, ps, 64)) { ok = false; break; }
-                    // packed row r: 128 bytes, 128B-swizzled by the TMA; group jg of the stage is its 16-byte chunks 4jg .. 4jg+3,
-                    // this half the chunks 4jg + 2h and 4jg + 2h + 1 (64 K-elements)
-                    const uint8_t *row = ld_ptr + ps * T::LOAD_STAGE_SMEM + r * 128;
-                    uint32_t a[32];
+                for (int c = 0; c < 2; c++) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(row + (((4 * jg + 2 * h + c) ^ (r & 7)) << 4));
+                    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        const uint4 v = *reinterpret_cast<const uint4 *>(row + (((4 * jg + 2 * h + c) ^ (r & 7)) << 4));
-                        const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {              // word i of chunk c = K-elements 32c + 8i .. +7 -> 4 column words
-                            uint32_t o[4];
-                            int4x8_to_bf16x8(words[i], o);
-                            a[16 * c + 4 * i] = o[0]; a[16 * c + 4 * i + 1] = o[1]; a[16 * c + 4 * i + 2] = o[2]; a[16 * c + 4 * i + 3] = o[3];
-                        }
+                    for (int i = 0; i < 4; i++) {              // word i of chunk c = K-elements 32c + 8i .. +7 -> 4 column words
+                        uint32_t o[4];
+                        int4x8_to_bf16x8(words[i], o);
+                        a[16 * c + 4 * i] = o[0]; a[16 * c + 4 * i + 1] = o[1]; a[16 * c + 4 * i + 2] = o[2]; a[16 * c + 4 * i + 3] = o[3];
                     }
-                    // the slot's A columns are free once the MMAs of the group that used them last are done
-                    if (!mbar_wait(gdone_bar(slot), sphase ^ 1u, abort_flag, p.status, ST_TIMEOUT_DEQUANT, 16 + slot, 64)) { ok = false; break; }
-                    tc_fence_after_sync();
-                    tmem_st_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(T::A_BASE + slot * T::A_COLS + 32 * h), a);
-                    tmem_st_wait();
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(ready_bar(slot));
                 }
-                if (!ok) break;
+                // the slot's A columns are free once the MMAs of the group that used them last are done
+                if (!mbar_wait(gdone_bar(slot), sphase ^ 1u, abort_flag, p.status, ST_TIMEOUT_DEQUANT, 16 + slot, 64)) { ok = false; break; }
+                tc_fence_after_sync();
+                tmem_st_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(T::A_BASE + slot * T::A_COLS + 32 * h), a);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ready_bar(slot));
             }
+            gcount0 += w.kb_count;
+            pcount0 += (w.kb_count + T::LOAD_GROUPS - 1) / T::LOAD_GROUPS;
         }
     } else {
         // ------------------------------------------------------------------ fold + epilogue

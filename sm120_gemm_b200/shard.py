@@ -120,7 +120,12 @@ class FusedNShardedGemm:
         a.x_scale_f = a.w_scale_f = 1.0
         a.y_num_peers, a.y_col_offset, a.y_ld = len(self.order), self.plan.row_start, self.N
         off = row0 * self.N * 2
-        for i, r in enumerate(self.order):
+        order = self.order
+        if self.multicast and order[0] != self.plan.rank:
+            # with a multicast address the first destination must be this rank's own matrix: the two-row-block kernels
+            # store a tile there first and forward it from there
+            order = [self.plan.rank] + [r for r in order if r != self.plan.rank]
+        for i, r in enumerate(order):
             a.y_peers[i] = ptrs[r] + off
         a.y_multicast = (mc + off) if self.multicast else None
         a.X, a.W, a.stream = X_ptr, W_ptr, stream

@@ -90,12 +90,15 @@ def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("kernel", KERNELS, ids=["tile256x256", "tile512x256"])
+@pytest.mark.parametrize("kernel,shape", [(KERNELS[0], (1024 + 64, 2048, 1536)), (KERNELS[1], (1024 + 64, 2048, 1536)),
+                                          (KERNELS[1], (2560 + 64, 8192, 512))], ids=["tile256x256", "tile512x256", "tile512x256_halved_last_wave"])
 @pytest.mark.parametrize("multicast", [False, True], ids=["peer_stores", "multicast_stores"])
-def test_two_gpu_sharded_equals_unsharded(tmp_path, multicast, kernel):
+def test_two_gpu_sharded_equals_unsharded(tmp_path, multicast, kernel, shape):
     import torch.multiprocessing as mp
 
-    world, M, N, K = 2, 1024 + 64, 2048, 1536       # M is not a tile multiple: the last row block is clipped (272 rows per host chunk)
+    # M is not a tile multiple: the last row block is clipped.  The third case gives every rank 6 x 16 = 96 tiles of 512 x 256
+    # on 74 clusters: the 22 tiles of the second round go out as 44 halves of 256 rows
+    world, (M, N, K) = 2, shape
     mp.spawn(_worker, args=(world, _free_port(), M, N, K, str(tmp_path), multicast, kernel), nprocs=world, join=True)
     used = []
     for r in range(world):
