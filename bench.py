@@ -32,9 +32,8 @@ ALTERNATE_FAMILY = ["bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1", "bf16_bm256_bn256
 CHECK_ROWS = 32
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel at this workload,
 # from the ncu capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES = {   # profiles/kernel_families_limited_metrics.md, 16384^3 rows
-    "bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1": 12197871872 + 531051008,
-    "bf16_bm256_bn256_bk64_s4_cg2_sk1_ab0_e1": 13662148608 + 537297664,
+NCU_TRAFFIC_BYTES = {   # profiles/kernel_families_limited_metrics.md, the 16384^3 row: 12 310.1 MB read + 531.9 MB written
+    "bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1": 12310100000 + 531900000,
 }
 
 
@@ -406,16 +405,16 @@ def main():
         flops = 2.0 * M * N * K
         peaks = load_peaks()
         value = flops * args.steps / (total_ms * 1e-3) / 1e12
-        # roofline of the dominant kernel (the tcgen05 GEMM): per-launch time = the step's event
-        # time at N=1 (one kernel per step); at N>1 the step also holds the all-gather, so the
-        # kernel-level figure is only reported for the single-GPU run
+        # roofline of the dominant kernel (the tcgen05 GEMM): per-launch time = the step's event time (one kernel per
+        # step and rank; at N>1 the kernel also sends its tiles to the other ranks and the step ends with a barrier,
+        # so the per-rank figure there is a lower bound on what the tensor pipe did)
         launch_ms = sum(per_step) / len(per_step)
         kflops = flops / world
         achieved = kflops / (launch_ms * 1e-3) / 1e12
-        roofline = {"bound": "tensor", "achieved": achieved if world == 1 else None, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["bf16_tflops"] if world == 1 else None, "traffic": NCU_TRAFFIC_BYTES.get(kern.config.name()) if world == 1 else None,
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES.get(kern.config.name()) if world == 1 else None,
                     "peak_source": f"{peaks['source']} (cuBLAS bf16 burst; sustained {peaks['bf16_tflops_sustained']})",
-                    "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if world == 1 and peaks["bf16_tflops_sustained"] else None,
+                    "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
                     "kernel": f"umma_gemm_kernel<{kern.config.name()}>", "flops_per_launch": kflops, "avg_launch_ms": launch_ms}
         clocks = sampler.result()
         ms_per_step = total_ms / args.steps

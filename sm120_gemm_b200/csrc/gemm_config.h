@@ -340,7 +340,12 @@ inline double heuristic_ms(const GemmConfig &c, int M, int N, int K, int sms = 1
         // + the FP32 partial tiles (two per CTA) written, read back and reduced by the fix-up kernel
         t = (tt > tm ? tt : tm) * (tiles < slots ? tiles / slots : 1.0) + 4.0 * slots * c.bm * c.bn * 4.0 / 5.0e12 + 4e-6;
     } else {
-        const double rounds = std::ceil(tiles * split / slots);
+        double rounds = std::ceil(tiles * split / slots);
+        if (c.bm == 256 * c.cg && c.split_k == 1 && tiles > slots) {
+            // two-row-block kernels deal the tiles of a last round that would leave half the clusters idle as halves
+            const double rest = tiles - std::floor(tiles / slots) * slots;
+            if (rest > 0 && 2.0 * rest <= slots) rounds -= 0.5;
+        }
         const double tt = unit_flops / slot_flops, tm = unit_bytes / slot_bw;
         t = rounds * (tt > tm ? tt : tm);
         if (c.split_k > 1) t += (4.0 * split + 2.0) * M * N / 5.0e12 + 3e-6;

@@ -144,6 +144,10 @@ def heuristic_ms(c: GemmConfig, M: int, N: int, K: int, sms: int = 148) -> float
         t = (tt if tt > tm else tm) * (tiles / slots if tiles < slots else 1.0) + 4.0 * slots * c.bm * c.bn * 4.0 / 5.0e12 + 4e-6
     else:
         rounds = float(math.ceil(tiles * split / slots))
+        if c.bm == 256 * c.cg and c.split_k == 1 and tiles > slots:
+            rest = tiles - math.floor(tiles / slots) * slots
+            if rest > 0 and 2.0 * rest <= slots:
+                rounds -= 0.5
         tt, tm = unit_flops / slot_flops, unit_bytes / slot_bw
         t = rounds * (tt if tt > tm else tm)
         if c.split_k > 1:
