@@ -48,6 +48,28 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         : "memory");
 }
 
+// 8 signed int4 (two's complement nibbles, nibble j = element j) -> four bf16x2 holding q / 64 exactly, with seven
+// integer-pipe instructions instead of nine.  Two lop3 mask the even and the odd nibbles of the word and flip their
+// sign bits (q + 8 in 0..15, one per byte); a prmt per output puts two of those bytes into the low bytes of the two
+// halves and zeroes above them (selector bit 3 replicates the byte's sign bit, which is clear): as bf16 that is the
+// subnormal (q + 8) * 2^-133, and fma.rn.bf16x2 with 2^127 and -1/8 turns it into (q + 8) / 64 - 8 / 64.  bf16
+// arithmetic keeps subnormal inputs (no flush-to-zero for this type), and every step is exact.  The fold multiplies
+// the totals by 64 at the end: a power of two, so the result is the one the integer-valued form gives, bit for bit.
+__device__ __forceinline__ void int4x8_to_bf16x8_div64(uint32_t w, uint32_t (&out)[4])
+{
+    uint32_t even, odd;
+    asm("lop3.b32 %0, %1, 0x0f0f0f0f, 0x08080808, 0x6A;" : "=r"(even) : "r"(w));
+    asm("lop3.b32 %0, %1, 0x0f0f0f0f, 0x08080808, 0x6A;" : "=r"(odd) : "r"(w >> 4));
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t sel = (uint32_t)j | ((8u | (uint32_t)j) << 4) | ((uint32_t)(4 + j) << 8) | ((8u | (uint32_t)(4 + j)) << 12);
+        uint32_t y;
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(y) : "r"(even), "r"(odd), "r"(sel));
+        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(out[j]) : "r"(y), "r"(0x7f007f00u), "r"(0xbe00be00u));   // * 2^127 - 1/8
+    }
+}
+constexpr float W4A16_TMEM_UNSCALE = 64.0f;
+
 __device__ __forceinline__ void tmem_st_wait()
 {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -275,7 +297,7 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
 #pragma unroll
                     for (int i = 0; i < 4; i++) {              // word i of chunk c = K-elements 32c + 8i .. +7 -> 4 column words
                         uint32_t o[4];
-                        int4x8_to_bf16x8(words[i], o);
+                        int4x8_to_bf16x8_div64(words[i], o);
                         a[16 * c + 4 * i] = o[0]; a[16 * c + 4 * i + 1] = o[1]; a[16 * c + 4 * i + 2] = o[2]; a[16 * c + 4 * i + 3] = o[3];
                     }
                 }
@@ -352,12 +374,12 @@ w4a16_tmem_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 if (n < p.N) {
 #pragma unroll
                     for (int m = 0; m < FC; m++)
-                        if (fg * FC + m < p.M) p.Y[(size_t)(fg * FC + m) * p.N + n] = __float2bfloat16_rn(total[m]);
+                        if (fg * FC + m < p.M) p.Y[(size_t)(fg * FC + m) * p.N + n] = __float2bfloat16_rn(total[m] * W4A16_TMEM_UNSCALE);
                 }
             } else {
                 float *slot = p.workspace + (size_t)(2 * cta + w.part) * 128 * 128 + (size_t)(fg * FC) * 128 + r;
 #pragma unroll
-                for (int m = 0; m < FC; m++) slot[m * 128] = total[m];
+                for (int m = 0; m < FC; m++) slot[m * 128] = total[m] * W4A16_TMEM_UNSCALE;
             }
         }
     }
