@@ -232,7 +232,7 @@ struct UmmaGemmTraits {
     static constexpr int ACC_STAGE_COLS = MB_ * ACC_STRIDE;  // TMEM columns of one accumulator stage (MB_ row blocks side by side)
     static constexpr int ACC_STAGES = (2 * ACC_STAGE_COLS + SF_COLS <= 512) ? 2 : 1;
     static constexpr int SF_RING_BYTES = (STAGES_ * SF_BYTES + 1023) / 1024 * 1024;   // keeps the staging tiles 1024-byte aligned
-    static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4;
+    static constexpr int NUM_BARRIERS = 2 * STAGES_ + 4 + (BLOCK_SCALED ? 4 : 0);   // block-scaled: + scale set ready / free, two sets
     static constexpr int RING_BYTES = STAGES_ * (A_BYTES + B_BYTES) + SF_RING_BYTES + NUM_BARRIERS * 8 + 16 + 1024;
     // Staging buffers of 128 rows x 64 bf16.  Two by default (one epilogue group: used in turn; two groups: one each).
     // A kernel with a single accumulator stage stalls its MMAs until the accumulator is drained, and with two
@@ -260,8 +260,10 @@ struct UmmaGemmTraits {
     static_assert(MB_ == 1 || (MB_ == 2 && SPLIT_K_ == 1 && EPI_ == EPI_TMA && !BLOCK_SCALED && ACC_STAGES == 1),
                   "two row blocks per CTA: whole-K tiles, TMA-store epilogue, dense operand kinds, one accumulator stage");
     static_assert(EPI_ != EPI_FUSED || (SPLIT_K_ == 1 && MB_ == 1), "the fused output transform works on whole-K tiles of one row block per CTA");
-    static_assert(STAGES_ >= 2, "at least two ring stages");
+    // (a 256 x 192 tile, whose scales start 64 rows into an atom on odd tiles -- two TMEM columns further on -- computes
+    // correctly and leaves room for two accumulator stages, but measured 4 % (MXFP8) and 12 % (MX-FP4) slower than 256 x 256)
     static_assert(!BLOCK_SCALED || BN_ % 128 == 0, "block-scaled tiles: BN a multiple of the 128-row scale atom");
+    static_assert(STAGES_ >= 2, "at least two ring stages");
     static_assert(ACC_COLS <= 512, "TMEM has 512 columns");
     static_assert(SMEM_ALLOC <= 232448, "exceeds the 227 KB of shared memory one CTA can have");
 };
@@ -290,6 +292,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    auto sfready_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 4 + s); };      // block-scaled kinds only
+    auto sffree_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 6 + s); };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (bar_base - smem_base) + 8u * T::NUM_BARRIERS);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     // epilogue -> senders: one counter per epilogue group (two words), the tiles whose row block that group has stored
@@ -311,6 +315,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         for (int a = 0; a < 2; a++) {
             mbar_init(tfull_bar(a), 1);
             mbar_init(tempty_bar(a), CG * 4 * T::EPI_GROUPS);   // one arrival per epilogue warp of every CTA of the group
+        }
+        if constexpr (T::BLOCK_SCALED) {
+            for (int s = 0; s < 2; s++) {
+                mbar_init(sfready_bar(s), 1);
+                mbar_init(sffree_bar(s), 1);
+            }
         }
         stored_count[0] = 0;
         stored_count[1] = 0;
@@ -411,24 +421,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (cta_rank == 0) {   // every lane runs the loop; one elected lane issues (see elect_one_sync)
             const uint32_t instr = (T::OPK == OPK_BF16) ? make_idesc(UMMA_BF16, UMMA_BF16, T::UMMA_M, BN)
                                                          : make_idesc(UMMA_E4M3, UMMA_E4M3, T::UMMA_M, BN);
-            // Scale factors live behind the accumulator buffers, in two sets used in turn (X atoms, then W atoms).  The
-            // smem -> TMEM copies of k-block i+1 are issued right after the MMAs of k-block i, so they run while those
-            // MMAs execute instead of standing between two k-blocks' MMAs (tcgen05 operations of one thread execute in
-            // order; a set is rewritten only after the MMAs that read it were issued).
+            // Scale factors live behind the accumulator buffers, in two sets used in turn (X atoms, then W atoms).  Warp 3
+            // copies them from shared memory (tcgen05.cp) one k-block ahead and publishes each set on sfready; this warp
+            // hands a set back on sffree once the MMAs that read it are done.
             const uint32_t sf_tmem0 = tmem_base + (uint32_t)(T::ACC_STAGES * T::ACC_STAGE_COLS);
-            int sf_set = 0;            // set the current k-block's MMAs read
-            bool sf_ready = false;     // its copies were already issued (as the previous k-block's look-ahead)
-            auto copy_scale_atoms = [&](int st, int set) {
-                const uint32_t sfa = sf_tmem0 + (uint32_t)(set * T::SF_COLS_ONE), sfb = sfa + (uint32_t)(T::SF_K_ATOMS * 4);
-                const uint32_t sf_src = sf_base + st * T::SF_BYTES;
-#pragma unroll
-                for (int a = 0; a < T::SF_K_ATOMS; a++) {
-                    tmem_cp_sf_atom<CG>(sfa + a * 4, make_sf_atom_desc(sf_src + a * 512));
-#pragma unroll
-                    for (int j = 0; j < T::SF_N_ATOMS; j++)
-                        tmem_cp_sf_atom<CG>(sfb + (a * T::SF_N_ATOMS + j) * 4, make_sf_atom_desc(sf_src + T::SF_A_BYTES + (a * T::SF_N_ATOMS + j) * 512));
-                }
-            };
+            uint32_t kcount = 0;       // k-blocks issued by this CTA so far: scale set kcount & 1
             int stage = 0;
             uint32_t phase = 0;
             int titer = 0;
@@ -446,14 +443,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         ok = false;
                         break;
                     }
+                    if constexpr (T::BLOCK_SCALED) {
+                        if (!__all_sync(0xffffffffu, mbar_wait(sfready_bar(kcount & 1u), (kcount >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, 32 + stage))) {
+                            ok = false;
+                            break;
+                        }
+                    }
                     tc_fence_after_sync();
                     if (elect_one_sync()) {
                     const uint64_t a_desc = make_smem_desc_k128(a_base + stage * T::A_BYTES);
                     const uint64_t b_desc = make_smem_desc_k128(b_base + stage * T::B_BYTES);
-                    const uint32_t sfa_tmem = sf_tmem0 + (uint32_t)(sf_set * T::SF_COLS_ONE), sfb_tmem = sfa_tmem + (uint32_t)(T::SF_K_ATOMS * 4);
-                    if constexpr (T::BLOCK_SCALED) {
-                        if (!sf_ready) copy_scale_atoms(stage, sf_set);
-                    }
+                    const uint32_t sfa_tmem = sf_tmem0 + (uint32_t)((kcount & 1u) * T::SF_COLS_ONE), sfb_tmem = sfa_tmem + (uint32_t)(T::SF_K_ATOMS * 4);
 #pragma unroll
                     for (int k = 0; k < T::UMMA_K_STEPS; k++) {
                         const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
@@ -482,30 +482,59 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                         }
                     }
                     if constexpr (CG == 1) umma_commit(empty_bar(stage)); else umma_commit_pair(empty_bar(stage), 3);
+                    if constexpr (T::BLOCK_SCALED) {
+                        if constexpr (CG == 1) umma_commit(sffree_bar(kcount & 1u)); else umma_commit_pair(sffree_bar(kcount & 1u), 1);
+                    }
                     }
                     __syncwarp();
+                    kcount++;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                    if constexpr (T::BLOCK_SCALED) {
-                        // look-ahead inside a tile: once the next k-block's bytes have landed, start its scale copies now
-                        sf_ready = false;
-                        if (kb + 1 < w.kb_count) {
-                            if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, stage))) {
-                                ok = false;
-                                break;
-                            }
-                            tc_fence_after_sync();
-                            sf_set ^= 1;
-                            if (elect_one_sync()) copy_scale_atoms(stage, sf_set);
-                            __syncwarp();
-                            sf_ready = true;
-                        }
-                    }
                 }
                 if (!ok) break;
                 if (elect_one_sync()) {
                     if constexpr (CG == 1) umma_commit(tfull_bar(acc)); else umma_commit_pair(tfull_bar(acc), 3);
                 }
                 __syncwarp();
+            }
+        }
+    } else if (warp == 3) {
+        // ------------------------------------------------------------------ scale-factor copier (block-scaled kinds)
+        if constexpr (T::BLOCK_SCALED) {
+            if (cta_rank == 0) {
+                const uint32_t sf_tmem0 = tmem_base + (uint32_t)(T::ACC_STAGES * T::ACC_STAGE_COLS);
+                int stage = 0;
+                uint32_t phase = 0, kcount = 0;
+                bool ok = true;
+                WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
+                WorkItem w;
+                while (ok && sched.next(w)) {
+                    for (int kb = 0; kb < w.kb_count; kb++, kcount++) {
+                        const uint32_t set = kcount & 1u;
+                        // the stage's scale atoms have landed, and the MMAs that read this set two k-blocks ago are done
+                        if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, 64 + stage)) ||
+                            !__all_sync(0xffffffffu, mbar_wait(sffree_bar(set), ((kcount >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_MMA_FULL, 96 + stage))) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        if (elect_one_sync()) {
+                            const uint32_t sfa = sf_tmem0 + set * (uint32_t)T::SF_COLS_ONE, sfb = sfa + (uint32_t)(T::SF_K_ATOMS * 4);
+                            const uint32_t sf_src = sf_base + stage * T::SF_BYTES;
+#pragma unroll
+                            for (int a = 0; a < T::SF_K_ATOMS; a++) {
+                                tmem_cp_sf_atom<CG>(sfa + a * 4, make_sf_atom_desc(sf_src + a * 512));
+#pragma unroll
+                                for (int j = 0; j < T::SF_N_ATOMS; j++)
+                                    tmem_cp_sf_atom<CG>(sfb + (a * T::SF_N_ATOMS + j) * 4,
+                                                        make_sf_atom_desc(sf_src + T::SF_A_BYTES + (a * T::SF_N_ATOMS + j) * 512));
+                            }
+                            // arrives once the copies above are complete (a commit tracks the issuing thread's tcgen05 operations)
+                            if constexpr (CG == 1) umma_commit(sfready_bar(set)); else umma_commit_pair(sfready_bar(set), 1);
+                        }
+                        __syncwarp();
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                }
             }
         }
     } else if (warp >= 4 && warp < 4 + 4 * T::EPI_GROUPS) {

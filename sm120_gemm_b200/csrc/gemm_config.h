@@ -101,7 +101,7 @@ struct GemmConfig {
         const size_t sf_ring = (num_stages * k_atoms * (1 + n_atoms) * 512 + 1023) / 1024 * 1024;
         const size_t mb = bm / (128 * cg) > 0 ? bm / (128 * cg) : 1;
         const size_t a = (size_t)128 * 128 * mb, b = (size_t)(bn / cg) * 128;
-        const size_t barriers = (2 * (size_t)num_stages + 4) * 8 + 16;
+        const size_t barriers = (2 * (size_t)num_stages + 4 + (k_atoms ? 4 : 0)) * 8 + 16;   // block-scaled: + scale set ready / free
         const size_t ring = num_stages * (a + b) + sf_ring + barriers + 1024;
         // a single accumulator stage (two do not fit in TMEM) gets four staging buffers when they fit
         const bool one_acc_stage = 2 * mb * (((size_t)bn + 31) / 32 * 32) + 2 * k_atoms * (1 + n_atoms) * 4 > 512;

@@ -86,7 +86,7 @@ class GemmConfig:
         n_atoms = -(-self.bn // 128)
         sf = k_atoms * (1 + n_atoms) * 512
         epi = 0 if self.split_k > 1 else self.epi
-        barriers = (2 * self.num_stages + 4) * 8 + 16
+        barriers = (2 * self.num_stages + 4 + (4 if k_atoms else 0)) * 8 + 16     # block-scaled: + scale set ready / free
         sf_ring = -(-self.num_stages * sf // 1024) * 1024
         ring = self.num_stages * (a + b) + sf_ring + barriers + 1024
         # one accumulator stage (two do not fit in the 512 TMEM columns beside the scale factors): four staging buffers if they fit
