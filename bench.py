@@ -260,17 +260,21 @@ def main():
 
     X, W, w_blocks = make_inputs(torch, dev, rank, world)
     Y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    kern = cands[0]
     fused_trial = fused_wanted and all(k.config.epi == 1 and k.config.split_k == 1 for k in cands)
-    if len(cands) > 1:
+    # on several GPUs a 256 x 256 plugin is tried both ways: sending from the epilogue, and forwarding tiles from L2
+    variants = [(k, False) for k in cands]
+    if fused_trial:
+        variants += [(k, True) for k in cands if k.config.bm == 256 and k.config.bn == 256 and k.config.cg == 2]
+    kern, forward = variants[0]
+    if len(variants) > 1:
         # Untimed selection trial.  On several GPUs the candidates are tried as the whole fused step (GEMM with
         # the gather in its epilogue, then the barrier).
         trial = []
         st = torch.cuda.current_stream().cuda_stream
-        for k in cands:
+        for k, fw in variants:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             if fused_trial:
-                f = FusedNShardedGemm(k, M, N, K, rank, world, double_buffer=False)
+                f = FusedNShardedGemm(k, M, N, K, rank, world, double_buffer=False, forward=fw)
                 run_once = lambda: f.run(X, W)
             else:
                 ya = torch.empty((M, plan_rows), dtype=torch.bfloat16, device=dev)
@@ -292,10 +296,10 @@ def main():
         t = torch.tensor(trial, device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)      # every rank must make the same choice
-        kern = cands[int(torch.argmin(t).item())]
+        kern, forward = variants[int(torch.argmin(t).item())]
     fused = fused_wanted and kern.config.epi == 1 and kern.config.split_k == 1
     if fused:
-        fop = FusedNShardedGemm(kern, M, N, K, rank, world)      # two symmetric result buffers used in turn
+        fop = FusedNShardedGemm(kern, M, N, K, rank, world, forward=forward)      # two symmetric result buffers used in turn
 
         class _Op:
             def run(self, X, W, Y):
@@ -425,7 +429,8 @@ def main():
             "config": {"workload": WORKLOAD, "kernel": kern.config.name(), "l2": "inputs larger than L2 (X, W, Y = 1.5 GiB vs 126 MB L2)",
                        "parallelism": "single GPU" if world == 1 else (
                            f"N-sharded x{world}: {plan_rows} weight rows per rank, all-gather fused into the epilogue "
-                           + ("(multimem stores to the NVSwitch multicast address of Y)" if fop.multicast else "(TMA stores to every rank's Y over NVLink)") + " + barrier"
+                           + (("(multimem stores to the NVSwitch multicast address of Y" + (", tiles forwarded from L2 by sender warps)" if (forward or kern.config.bm == 512) else ", sent from the epilogue)"))
+                              if fop.multicast else "(TMA stores to every rank's Y over NVLink)") + " + barrier"
                            if fused else f"N-sharded x{world}: {plan_rows} weight rows per rank + NCCL all-gather + interleave")},
             "roofline": roofline,
             "e2e": {"value": flops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,

@@ -108,6 +108,11 @@ typedef struct GemmArgs {
     float y_scale;          /* e4m3 output: multiplies D before the conversion                                     */
     float *amax;            /* device float, optional: atomically raised to max|D| (before y_scale); the caller    */
                             /* zeroes it before the first launch that should count                                 */
+    /* With y_multicast, 256 x 256 TMA-store plugins (`_bm256_bn256_..._cg2_sk1_..._e1`, bf16 and fp8): 0 = the      */
+    /* epilogue sends 128-byte row pieces to the multicast address; 1 = it stores the tile to y_peers[0] (this GPU's */
+    /* own matrix) and four sender warps forward whole 512-byte rows from L2 while the next tile is computed.  The   */
+    /* 512 x 256 plugins always forward; every other plugin ignores the field.                                      */
+    int32_t y_forward;
 } GemmArgs;
 
 enum { GEMM_ACT_NONE = 0, GEMM_ACT_RELU = 1, GEMM_ACT_GELU = 2 /* erf form */, GEMM_ACT_SILU = 3 };

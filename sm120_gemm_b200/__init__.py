@@ -52,6 +52,7 @@ class GemmArgs(ctypes.Structure):
         ("y_peers", ctypes.c_void_p * 8), ("y_multicast", ctypes.c_void_p),
         ("C", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
         ("activation", ctypes.c_int32), ("y_dtype", ctypes.c_int32), ("y_scale", ctypes.c_float), ("amax", ctypes.c_void_p),
+        ("y_forward", ctypes.c_int32),
     ]
 
     def __init__(self, *a, **kw):

@@ -85,6 +85,8 @@ struct YTarget {
     long long ld = 0;               // row pitch of the destination matrices in elements
     int col_offset = 0;
     void *multicast = nullptr;      // NVSwitch multicast address of the same matrix: one multimem store reaches every rank
+    bool forward = false;           // with a multicast address, kernels that have sender warps: store the tile locally and let
+                                    // them forward it (two-row-block kernels always do)
 };
 
 struct GemmParams {
@@ -112,6 +114,7 @@ struct GemmParams {
     float *amax;          // nullptr = not wanted
     int act;              // ACT_*
     int y_dtype;          // YOUT_*
+    int forward;          // N-sharded run with a multicast address: 1 = tiles go to the local matrix and the sender warps forward them
     int tail_full;        // two-row-block kernels: whole tiles before the halved last wave (see WorkSched); < 0: no halving
     int test_withhold_kb; // wait-expiry test build only: the producer stops before this k-block (< 0: never)
 };
@@ -251,7 +254,9 @@ struct UmmaGemmTraits {
     // tile; in an N-sharded run its multicast stores would be paced by NVLink (a few GB/s per SM).  Such kernels
     // therefore store the tile to the LOCAL result with TMA stores and four more warps ("senders") forward finished
     // tiles from there to the multicast address while the next tile's MMAs run.
-    static constexpr int SENDER_WARPS = (MB_ == 2) ? 4 : 0;
+    // The 256 x 256 TMA-store kernels carry the sender warps too: there the caller chooses between sending 128-byte row
+    // pieces from the epilogue and forwarding whole 512-byte rows from L2 (GemmParams::forward).
+    static constexpr int SENDER_WARPS = (MB_ == 2 || (CG_ == 2 && BN_ == 256 && EPI == EPI_TMA && SPLIT_K_ == 1 && !BLOCK_SCALED)) ? 4 : 0;
     static constexpr int THREADS = 128 + 128 * EPI_GROUPS + 32 * SENDER_WARPS;
     static_assert(BN_ % 16 == 0 && BN_ >= 16 && BN_ <= 256, "BN (the UMMA N extent) is a multiple of 16 up to 256");
     static_assert(EPI != EPI_TMA || BN_ % 64 == 0, "the TMA-store epilogue writes 64-column boxes");
@@ -580,7 +585,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             if (half && eg == 1) {
                 release_acc();
                 if constexpr (T::SENDER_WARPS > 0) {
-                    if (p.y_mc != nullptr && epi_tid == 0) smem_counter_add_release(smem_u32(const_cast<uint32_t *>(stored_count + eg)));
+                    if (p.forward && epi_tid == 0) smem_counter_add_release(smem_u32(const_cast<uint32_t *>(stored_count + eg)));
                 }
             } else if (T::SPLIT_K == 0 && w.part >= 0) {
                 // stream-K partial: the CTA's private slot, tile-local [BM][BN] layout, no bounds
@@ -645,7 +650,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     if (j + J_STEP >= BN / 64) release_acc();       // this group's last piece of the accumulator
                     fence_proxy_async_smem();
                     named_bar_sync(bar_a, 128);
-                    if (T::SENDER_WARPS == 0 && p.y_mc != nullptr) {
+                    if (p.y_mc != nullptr && !(T::SENDER_WARPS > 0 && p.forward)) {
                         // all-gather through NVSwitch: eight lanes read one staged 128-byte row piece and store it
                         // once to the multicast address (16 rows per pass); the barrier at the top of the next
                         // round keeps writers off this buffer until every reader is done
@@ -670,7 +675,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 if constexpr (T::SENDER_WARPS > 0) {
                     // N-sharded run: this group's row block of the tile is on its way to the local result; once the
                     // stores are complete the senders may read it back (from L2) and forward it to the other ranks
-                    if (p.y_mc != nullptr && epi_tid == 0) {
+                    if (p.forward && epi_tid == 0) {
                         tma_store_wait<0>();
                         fence_proxy_async_global();
                         smem_counter_add_release(smem_u32(const_cast<uint32_t *>(stored_count + eg)));
@@ -781,9 +786,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             if (epi_tid == 0) tma_store_wait<0>();
         }
     } else if (warp >= 4 + 4 * T::EPI_GROUPS) {
-        // ------------------------------------------------------------------ senders (two-row-block kernels, N-sharded run)
+        // ------------------------------------------------------------------ senders (N-sharded run, tiles forwarded from L2)
         if constexpr (T::SENDER_WARPS > 0) {
-            if (p.y_mc != nullptr) {
+            if (p.forward) {
                 const int st = threadIdx.x - (128 + 128 * T::EPI_GROUPS);    // 0 .. 127
                 const int chunk = st & 31;                                    // 16-byte piece of a 512-byte tile row
                 const bf16 *local = static_cast<const bf16 *>(p.Y);          // this rank's own copy of the result
@@ -797,9 +802,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     const int m0 = half ? mb * T::BM + w.half * (T::BM / 2) + (int)cta_rank * 128 : mb * T::BM + (int)cta_rank * T::BM_CTA;
                     const int rows = half ? 128 : T::BM_CTA;
                     const int col = nb * BN + chunk * 8;
-                    // work item number titer is stored once both groups have counted it
+                    // work item number titer is stored once every epilogue group has counted it
                     if (!smem_counter_wait(smem_u32(const_cast<uint32_t *>(stored_count)), (uint32_t)(titer + 1), abort_flag, p.status, ST_TIMEOUT_EPILOGUE, 8) ||
-                        !smem_counter_wait(smem_u32(const_cast<uint32_t *>(stored_count + 1)), (uint32_t)(titer + 1), abort_flag, p.status, ST_TIMEOUT_EPILOGUE, 9))
+                        (T::EPI_GROUPS == 2 &&
+                         !smem_counter_wait(smem_u32(const_cast<uint32_t *>(stored_count + 1)), (uint32_t)(titer + 1), abort_flag, p.status, ST_TIMEOUT_EPILOGUE, 9)))
                         break;
                     if (col + 8 > p.N) continue;
                     const size_t off0 = (size_t)p.y_col_offset + col;
@@ -1114,7 +1120,7 @@ struct UmmaGemmLauncher {
                 return set_error(GEMM_ERR_ARG, "multicast stores need N %% 8 == 0 and a 16-byte aligned address");
             y_targets = 0;
             tys.m[0] = tx;
-            if (T::SENDER_WARPS > 0) {
+            if (T::SENDER_WARPS > 0 && (T::MB == 2 || yt->forward)) {
                 // the tile goes to this rank's own matrix first (peers[0], by contract the local one when a multicast
                 // address is given); the sender warps forward it from there
                 if (!yt->peers[0]) return set_error(GEMM_ERR_ARG, "null local destination (y_peers[0])");
@@ -1149,7 +1155,8 @@ struct UmmaGemmLauncher {
         p.group_n = band_width(T::BN, T::MB);
         // with a single accumulator stage the epilogue's wake-up is on the critical path of every tile
         p.wait_sleep_ns = wait_sleep_ns(T::ACC_STAGES == 1 ? (p.num_k_blocks < 16 ? p.num_k_blocks : 16) : p.num_k_blocks);
-        p.Y = (fused_gather && yt->multicast && T::SENDER_WARPS > 0) ? yt->peers[0] : Y;
+        p.forward = (fused_gather && yt->multicast && T::SENDER_WARPS > 0 && (T::MB == 2 || yt->forward)) ? 1 : 0;
+        p.Y = p.forward ? yt->peers[0] : Y;
         p.workspace = workspace;
         p.alpha = alpha;
         p.status = dev->status;

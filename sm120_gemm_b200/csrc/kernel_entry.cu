@@ -115,6 +115,7 @@ int gemm_run_ex(const GemmArgs *a)
     yt.peers = a->y_peers;
     yt.num_peers = a->y_num_peers;
     yt.multicast = a->y_multicast;
+    yt.forward = a->y_forward != 0;
     yt.ld = a->y_ld;
     yt.col_offset = a->y_col_offset;
     sm100::LaunchExtras ex;

@@ -70,7 +70,7 @@ class FusedNShardedGemm:
     and ``run`` opens with a barrier of its own instead (every rank is done with the previous result first)."""
 
     def __init__(self, kernel, M: int, N: int, K: int, rank: int, world: int, group=None, rotate: bool = True, peers=None,
-                 multicast: bool = True, double_buffer: bool = True):
+                 multicast: bool = True, double_buffer: bool = True, forward: bool = False):
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
@@ -87,6 +87,9 @@ class FusedNShardedGemm:
             raise ValueError(f"{kernel.config.name()} cannot run the {M}x{self.plan.rows}x{K} shard")
         dev = torch.device("cuda", torch.cuda.current_device())
         self.double_buffer = bool(double_buffer)
+        # multicast runs of the 256 x 256 plugins: store each tile locally and let the kernel's sender warps forward it
+        # from L2 in 512-byte rows, instead of sending 128-byte pieces from the epilogue (the 512 x 256 plugins always forward)
+        self.forward = bool(forward)
         self.buffers, self.handles, self.args_list = [], [], []
         # Destination order: own buffer first, then rank+1, rank+2, ... so that at any moment the ranks
         # (which walk their tiles in step) send to eight different GPUs instead of all to the same one.
@@ -128,6 +131,7 @@ class FusedNShardedGemm:
         for i, r in enumerate(order):
             a.y_peers[i] = ptrs[r] + off
         a.y_multicast = (mc + off) if self.multicast else None
+        a.y_forward = 1 if (self.multicast and self.forward) else 0
         a.X, a.W, a.stream = X_ptr, W_ptr, stream
         return a
 

@@ -21,7 +21,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel):
+def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel, forward):
     import torch.distributed as dist
 
     import sm120_gemm_b200 as g
@@ -49,7 +49,7 @@ def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel):
     g.dispatch(k, M, N, K, X2.data_ptr(), W.data_ptr(), Yref2.data_ptr(), 0, st)
     ok = []
     for double_buffer in (True, False):
-        fused = FusedNShardedGemm(k, M, N, K, rank, world, multicast=multicast, double_buffer=double_buffer)
+        fused = FusedNShardedGemm(k, M, N, K, rank, world, multicast=multicast, double_buffer=double_buffer, forward=forward)
         for b in fused.buffers:
             b.fill_(float("nan"))
         dist.barrier()
@@ -90,16 +90,17 @@ def _worker(rank, world, port, M, N, K, out_dir, multicast, kernel):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("kernel,shape", [(KERNELS[0], (1024 + 64, 2048, 1536)), (KERNELS[1], (1024 + 64, 2048, 1536)),
-                                          (KERNELS[1], (2560 + 64, 8192, 512))], ids=["tile256x256", "tile512x256", "tile512x256_halved_last_wave"])
+@pytest.mark.parametrize("kernel,shape,forward", [(KERNELS[0], (1024 + 64, 2048, 1536), False), (KERNELS[0], (1024 + 64, 4096, 1536), True),
+                                                  (KERNELS[1], (1024 + 64, 2048, 1536), False), (KERNELS[1], (2560 + 64, 8192, 512), False)],
+                         ids=["tile256x256", "tile256x256_forwarded_from_l2", "tile512x256", "tile512x256_halved_last_wave"])
 @pytest.mark.parametrize("multicast", [False, True], ids=["peer_stores", "multicast_stores"])
-def test_two_gpu_sharded_equals_unsharded(tmp_path, multicast, kernel, shape):
+def test_two_gpu_sharded_equals_unsharded(tmp_path, multicast, kernel, shape, forward):
     import torch.multiprocessing as mp
 
     # M is not a tile multiple: the last row block is clipped.  The third case gives every rank 6 x 16 = 96 tiles of 512 x 256
     # on 74 clusters: the 22 tiles of the second round go out as 44 halves of 256 rows
     world, (M, N, K) = 2, shape
-    mp.spawn(_worker, args=(world, _free_port(), M, N, K, str(tmp_path), multicast, kernel), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), M, N, K, str(tmp_path), multicast, kernel, forward), nprocs=world, join=True)
     used = []
     for r in range(world):
         ok = np.load(tmp_path / f"ok_{r}.npy")
