@@ -137,7 +137,7 @@ struct WorkItem {
 //
 // Halved last wave (SPLIT_K == 1, two-row-block kernels only; p.tail_full >= 0): when the tiles left for the last
 // round of the grid are at most half as many as the clusters, every one of them is dealt as two halves of 256 rows,
-// each computed like a 256 x 256 tile by a cluster of its own, so the last round takes half as long.  Virtual
+// each computed like a 256 x 256 tile by a cluster of its own, so the last wave takes half as long.  Virtual
 // indices below tail_full are whole tiles; index tail_full + 2i + h is half h of tile tail_full + i.
 template <int SPLIT_K>
 struct WorkSched {
@@ -1180,7 +1180,7 @@ struct UmmaGemmLauncher {
         if (rc != GEMM_OK) return rc;
         p.tail_full = -1;
         if (T::MB == 2 && T::SPLIT_K == 1) {
-            // the tiles of the last round, when they would leave at least half of the clusters idle, go out as halves
+            // the tiles of the last wave, when they would leave at least half of the clusters idle, go out as halves
             int full_grid = 0;
             rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &full_grid, false);
             if (rc != GEMM_OK) return rc;

@@ -342,7 +342,7 @@ inline double heuristic_ms(const GemmConfig &c, int M, int N, int K, int sms = 1
     } else {
         double rounds = std::ceil(tiles * split / slots);
         if (c.bm == 256 * c.cg && c.split_k == 1 && tiles > slots) {
-            // two-row-block kernels deal the tiles of a last round that would leave half the clusters idle as halves
+            // two-row-block kernels deal the tiles of a last wave that would leave half the clusters idle as halves
             const double rest = tiles - std::floor(tiles / slots) * slots;
             if (rest > 0 && 2.0 * rest <= slots) rounds -= 0.5;
         }
