@@ -279,12 +279,13 @@ def main():
             else:
                 ya = torch.empty((M, plan_rows), dtype=torch.bfloat16, device=dev)
                 run_once = lambda: g.dispatch(k, M, plan_rows, K, X.data_ptr(), W.data_ptr(), ya.data_ptr(), 0, st)
-            run_once()
+            for _ in range(3):
+                run_once()
             if world > 1:
                 dist.barrier()
             torch.cuda.synchronize()
             e0.record()
-            for _ in range(3):
+            for _ in range(8):      # long enough to be judged at the clocks the power cap allows, as the timed steps are
                 run_once()
             e1.record()
             torch.cuda.synchronize()
