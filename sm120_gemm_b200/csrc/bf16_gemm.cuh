@@ -115,6 +115,7 @@ struct GemmParams {
     int act;              // ACT_*
     int y_dtype;          // YOUT_*
     int forward;          // N-sharded run with a multicast address: 1 = tiles go to the local matrix and the sender warps forward them
+    uint32_t *wave_sync;  // two-row-block kernels, many waves: arrival counter that keeps the clusters' producers in step (or nullptr)
     int tail_full;        // two-row-block kernels: whole tiles before the halved last wave (see WorkSched); < 0: no halving
     int test_withhold_kb; // wait-expiry test build only: the producer stops before this k-block (< 0: never)
 };
@@ -377,6 +378,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             uint32_t phase = 0;
             const uint32_t full_leader = (CG == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
             bool ok = true;
+            int pace_iter = 0;             // work items this producer has started
+            uint32_t pace_target = 0;      // arrivals that complete the current wave's count
             WorkSched<T::SPLIT_K> sched(cluster_id, num_clusters, p);
             WorkItem w;
             while (ok && sched.next(w)) {
@@ -388,6 +391,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 const int row_w = nb * BN + (int)cta_rank * T::BN_CTA;
                 const uint32_t stage_bytes = half ? T::STAGE_BYTES - T::A_BYTES / 2 : T::STAGE_BYTES;
                 SM100_BOUNDS(row_x >= 0 && row_x < p.M + T::BM && row_w >= 0 && row_w < p.N + BN, ST_BOUNDS_LOAD_ROW, w.tile);
+                if constexpr (T::MB == 2) {
+                    // Wave pacing.  Clusters that share an operand panel read it from DRAM once only while they stay within
+                    // the few dozen microseconds a line survives in L2; left alone they drift apart over the waves of a
+                    // long launch (measured: one wave reads exactly its unique bytes, 28 waves read 1.9 times theirs).
+                    // Before its second and later tiles the leader's producer therefore counts itself in and waits until
+                    // every cluster that has such a tile has done so too -- or 40 microseconds have passed: the wait
+                    // only paces, nothing depends on it, and a cluster that is not running cannot hold the others up.
+                    if (p.wave_sync != nullptr && cta_rank == 0 && pace_iter > 0) {
+                        const long long tiles = (long long)p.num_m_blocks * p.num_n_blocks;
+                        const long long left = tiles - (long long)pace_iter * num_clusters;
+                        pace_target += (uint32_t)(left < num_clusters ? left : num_clusters);
+                        atomicAdd(p.wave_sync, 1u);
+                        const long long t0 = clock64();
+                        uint32_t seen;
+                        do {
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.wave_sync) : "memory");
+                            if (seen >= pace_target) break;
+                            __nanosleep(200);
+                        } while (clock64() - t0 < 80000);
+                    }
+                    pace_iter++;
+                }
                 for (int kb = 0; kb < w.kb_count; kb++) {
                     const int kx = (w.kb_begin + kb) * T::BK_COORD;
                     // tensor-map element = bf16, or one byte for the 8- and 4-bit kinds: the box must start inside the
@@ -956,7 +981,10 @@ inline int wait_sleep_ns(int num_k_blocks)
 // Width of a rasterisation band in tiles.
 inline int band_width(int bn, int mb = 1)
 {
-    if (mb == 2) return 16;      // 512-row tiles: a band of 16 x 256 columns keeps a wave about square
+    // 512-row tiles: measured at 16384^3 over forty back-to-back launches (power-capped clocks), mean of six runs each:
+    // 16 columns 6.53 ms (one run in six at 6.02, the others 6.55-6.74), 14 columns 6.20 ms (6.12-6.31), 12 columns
+    // 6.27 ms, 10 columns 6.29 ms, 8 columns 6.85 ms, 32 columns 6.68 ms; the library GEMM took 6.01-6.06 ms beside them
+    if (mb == 2) return 14;
     return bn >= 256 ? 8 : 16;
 }
 
@@ -1179,6 +1207,7 @@ struct UmmaGemmLauncher {
         rc = grid_size(*dev, work > (1 << 30) ? (1 << 30) : (int)work, sm_limit, &grid, M >= 512);
         if (rc != GEMM_OK) return rc;
         p.tail_full = -1;
+        p.wave_sync = nullptr;
         if (T::MB == 2 && T::SPLIT_K == 1) {
             // the tiles of the last wave, when they would leave at least half of the clusters idle, go out as halves
             int full_grid = 0;
@@ -1190,6 +1219,11 @@ struct UmmaGemmLauncher {
             if (tiles > clusters && rest > 0 && 2 * rest <= clusters) {
                 p.tail_full = tiles - rest;
                 grid = full_grid;
+            } else if (tiles >= 4 * (grid / T::CG)) {
+                // four waves or more: pace the clusters (see the producer); the counter is zeroed in stream order
+                uint32_t *slot = dev->wave_sync + dev->wave_next.fetch_add(1, std::memory_order_relaxed) % WAVE_SYNC_SLOTS;
+                SM100_CUDA_TRY(cudaMemsetAsync(slot, 0, sizeof(uint32_t), stream));
+                p.wave_sync = slot;
             }
         }
         if (T::SPLIT_K == 0 && grid > STREAMK_MAX_CTAS) grid = STREAMK_MAX_CTAS - STREAMK_MAX_CTAS % T::CG;

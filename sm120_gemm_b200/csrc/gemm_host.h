@@ -66,12 +66,18 @@ struct DeviceInfo {
     int max_smem_optin = 0;
     int cc_major = 0;
     uint32_t *status = nullptr;  // device address of the plugin's status block
+    uint32_t *wave_sync = nullptr;        // device address of g_wave_sync
+    std::atomic<unsigned> wave_next{0};   // next slot of g_wave_sync to hand to a launch
 };
 
 static constexpr int MAX_DEVICES = 32;
 
 // the status block: [0] code, [1] blockIdx.x, [2] detail, [3] spare
 __device__ uint32_t g_status_block[4];
+// Arrival counters for launches whose clusters pace themselves wave by wave (one word per launch in flight, handed
+// out in turn and zeroed on the launch's stream just before the kernel).
+static constexpr int WAVE_SYNC_SLOTS = 64;
+__device__ uint32_t g_wave_sync[WAVE_SYNC_SLOTS];
 
 inline int device_info(DeviceInfo **out)
 {
@@ -93,6 +99,8 @@ inline int device_info(DeviceInfo **out)
             SM100_CUDA_TRY(cudaGetSymbolAddress(&p, g_status_block));
             SM100_CUDA_TRY(cudaMemset(p, 0, sizeof(uint32_t) * 4));
             d.status = static_cast<uint32_t *>(p);
+            SM100_CUDA_TRY(cudaGetSymbolAddress(&p, g_wave_sync));
+            d.wave_sync = static_cast<uint32_t *>(p);
             d.ready.store(true, std::memory_order_release);
         }
     }
