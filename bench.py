@@ -32,8 +32,9 @@ ALTERNATE_FAMILY = ["bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1", "bf16_bm512_bn256
 CHECK_ROWS = 32
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel at this workload,
 # from the ncu capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES = {   # profiles/kernel_families_limited_metrics.md, the 16384^3 row: 12 310.1 MB read + 531.9 MB written
-    "bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1": 12310100000 + 531900000,
+NCU_TRAFFIC_BYTES = {   # profiles/kernel_families_limited_metrics.md, the 16384^3 rows (read + written, with wave pacing)
+    "bf16_bm512_bn256_bk64_s3_cg2_sk1_ab0_e1": 6492843520 + 527142400,
+    "bf16_bm512_bn256_bk64_s4_cg2_sk1_ab0_e1": 6492905472 + 528000000,
 }
 
 
