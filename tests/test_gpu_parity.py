@@ -94,7 +94,7 @@ def test_two_row_blocks_per_cta_bit_identical(registry, cuda_device):
     assert tall is not None and base is not None
     # the last two leave 6 and 11 tiles for the second round of the 74 clusters: those go out as halves of 256 rows
     for (M, N, K) in [(2048, 1024, 2048), (1000, 520, 1088), (513, 264, 64), (4096 + 384, 2048 + 8, 4096), (2560, 4096, 512), (2400, 4104, 320),
-                      (8192, 8192, 256)]:       # 512 tiles, seven waves: the producers pace themselves wave by wave
+                      (8192, 8192, 4096)]:      # 512 tiles of 64 k-blocks, seven waves: the producers pace themselves wave by wave
         X, W = o.make_inputs(M, N, K, seed=7 * M + N + K)
         Xd, Wd = to_dev(X), to_dev(W)
         a, b = to_bits(run_bf16(tall, Xd, Wd)), to_bits(run_bf16(base, Xd, Wd))
