@@ -305,6 +305,10 @@ def main():
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)      # every rank must make the same choice
         kern, forward = variants[int(torch.argmin(t).item())]
+        if rank == 0:       # the trial's table, for the record (stderr: stdout carries the one JSON line)
+            n_timed = max(3, min(args.steps, 40))
+            for (k, fw), ms in zip(variants, t.tolist()):
+                sys.stderr.write(f"trial: {k.config.name()}{' forwarded from L2' if fw else ''}: {ms / n_timed:.4f} ms per step\n")
     fused = fused_wanted and kern.config.epi == 1 and kern.config.split_k == 1
     if fused:
         fop = FusedNShardedGemm(kern, M, N, K, rank, world, forward=forward)      # two symmetric result buffers used in turn
